@@ -10,7 +10,7 @@ Python entry point::
 The model class is chosen by ``architectures[0]`` of config.json through the
 registry in :mod:`airun_b200.config`.
 """
-from .config import (ConfigError, ModelConfig, Qwen3Config, load_config, register_architecture,
+from .config import (ConfigError, ModelConfig, Qwen3Config, VedizenConfig, load_config, register_architecture,
                      registered_architectures)
 from .engine.engine import Engine, EngineOptions, GenerationResult, GenerationStats
 from .engine.step import StepEntry, StepRunner
@@ -19,5 +19,5 @@ from .sampling.sampler import SamplingParams
 from .weights import WeightError, write_model_folder
 
 __all__ = ["Engine", "EngineOptions", "GenerationResult", "GenerationStats", "SamplingParams", "StepEntry",
-           "StepRunner", "ConfigError", "WeightError", "ModelConfig", "Qwen3Config", "load_config",
+           "StepRunner", "ConfigError", "WeightError", "ModelConfig", "Qwen3Config", "VedizenConfig", "load_config",
            "register_architecture", "registered_architectures", "register_part", "write_model_folder"]

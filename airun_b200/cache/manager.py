@@ -428,8 +428,12 @@ class CacheStorage:
 
     def __init__(self, manager: CacheManager, dtype: torch.dtype, device):
         self.manager = manager
-        self.paged = [torch.zeros((len(g.owners), manager.num_pages, 2, g.spec.num_kv_heads,
-                                   manager.page_size, g.spec.head_dim), dtype=dtype, device=device)
+        # a page is [2, kv_heads, page_size, head_dim]; where values have a size of their own it is flat:
+        # the keys [kv_heads, page_size, head_dim], then the values [kv_heads, page_size, value_dim]
+        self.paged = [torch.zeros((len(g.owners), manager.num_pages) + (
+                                      (2, g.spec.num_kv_heads, manager.page_size, g.spec.head_dim)
+                                      if g.spec.v_dim == g.spec.head_dim else
+                                      (manager.page_size * g.spec.elements_per_token(),)), dtype=dtype, device=device)
                       for g in manager.paged]
         self.state = [torch.zeros((len(g.owners), manager.max_requests) + tuple(g.spec.shape),
                                   dtype=g.spec.dtype, device=device) for g in manager.state]

@@ -43,10 +43,13 @@ class LayerCall:
     ``layer`` indexes the model's layer list (the same layer may be named by
     several entries).  ``cache_from`` is None when the entry owns a cache of its
     own, or the index of an earlier entry of the order whose cache it reads
-    instead of writing one.
+    instead of writing one.  ``add_row`` names a row of the configuration's ``order_table()`` (a
+    [rows, hidden] tensor of the model) that is added to every token of the residual stream right before
+    this entry runs: the offset of a pass over layers that run several times.
     """
     layer: int
     cache_from: Optional[int] = None
+    add_row: Optional[int] = None     # row of the model's order table added to the residual stream before this entry
 
 
 class ModelConfig:
@@ -114,11 +117,29 @@ def architecture_name(d: Dict[str, Any]) -> str:
     archs = d.get("architectures")
     if isinstance(archs, list) and archs and isinstance(archs[0], str):
         return archs[0]
-    raise ConfigError("config.json is missing 'architectures' (a list whose first entry names the model class)")
+    if isinstance(d.get("architecture"), str) and d["architecture"]:
+        return d["architecture"]
+    raise ConfigError("config.json is missing 'architectures' (a list whose first entry names the model class) "
+                      "or 'architecture' (its name)")
 
 
-def load_config(model_dir: str) -> ModelConfig:
-    """config.json of ``model_dir`` as the typed configuration of its architecture."""
+def load_config(model_dir: str, tensor_shapes: Optional[Dict[str, Tuple[int, ...]]] = None) -> ModelConfig:
+    """config.json of ``model_dir`` as the typed configuration of its architecture.  An architecture some of
+    whose sizes only the tensors' shapes give (``with_tensor_shapes``) is completed from ``tensor_shapes``
+    (name -> shape), or from the headers of the folder's safetensors files when there are any."""
     d = read_config_json(model_dir)
     config_cls, _ = lookup_architecture(architecture_name(d))
-    return config_cls.from_dict(d)
+    config = config_cls.from_dict(d)
+    if hasattr(config, "with_tensor_shapes"):
+        if tensor_shapes is None:
+            from ..weights.loader import open_model_folder
+            try:
+                src = open_model_folder(model_dir)
+            except Exception:       # noqa: BLE001 - a folder without weights: the configuration's own defaults stand
+                return config
+            try:
+                tensor_shapes = {n: tuple(src.info(n)[1]) for n in src.names()}
+            finally:
+                src.close()
+        config = config.with_tensor_shapes(tensor_shapes)
+    return config

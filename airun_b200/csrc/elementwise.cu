@@ -397,3 +397,101 @@ AIRUN_EXPORT int airun_copy_pages(void* pool, int owners, int num_pages, long lo
                                                                  page_bytes / 16, pairs, num_pages, err);
     return airun_launch_status();
 }
+
+// Dynamic Tanh norm, which takes no statistic of the row: out = tanh(alpha * v) * w + b with
+// v = x [+ delta] [+ vec], alpha one number for the whole norm (read from device memory), w and b
+// vectors.  `vec` is one row added to every token (a per-pass offset of the residual stream).  With
+// write_back the sum v becomes the new x.  Source row = rows ? rows[r] : r.  The accurate tanhf is used.
+template <typename TOut>
+__global__ void dyt_norm_kernel(float* __restrict__ x, const float* __restrict__ delta, const float* __restrict__ vec,
+                                const float* __restrict__ alpha, const float* __restrict__ w, const float* __restrict__ b,
+                                TOut* __restrict__ out, const int32_t* __restrict__ rows, int n, int write_back) {
+    pdl_trigger();
+    pdl_wait();
+    const int r = blockIdx.x;
+    const int src = rows ? rows[r] : r;
+    const float a = alpha[0];
+    float* xr = x + (size_t)src * n;
+    const float* dr = delta ? delta + (size_t)src * n : nullptr;
+    TOut* outr = out + (size_t)r * n;
+    for (int i = blockIdx.y * blockDim.x + threadIdx.x; i < n; i += gridDim.y * blockDim.x) {
+        float v = xr[i];
+        if (dr) v += dr[i];
+        if (vec) v += vec[i];
+        if (write_back) xr[i] = v;
+        outr[i] = from_f32<TOut>(fmaf(tanhf(a * v), w[i], b[i]));
+    }
+}
+
+AIRUN_EXPORT int airun_dyt_norm(float* x, const float* delta, const float* vec, const float* alpha, const float* w,
+                                const float* b, void* out, int out_dtype, const int32_t* rows, int n_rows, int n,
+                                int write_back, cudaStream_t stream) {
+    if (n_rows < 0 || n <= 0 || !alpha || !w || !b) return AIRUN_ERR_ARG;
+    if (n_rows == 0) return AIRUN_OK;
+    const int threads = 256;
+    dim3 grid(n_rows, min(ceil_div_i(n, threads), 64));
+    if (out_dtype == AIRUN_DT_F32)
+        airun_launch(dyt_norm_kernel<float>, grid, dim3(threads), 0, stream, x, delta, vec, alpha, w, b, (float*)out, rows, n, write_back);
+    else if (out_dtype == AIRUN_DT_BF16)
+        airun_launch(dyt_norm_kernel<__nv_bfloat16>, grid, dim3(threads), 0, stream, x, delta, vec, alpha, w, b, (__nv_bfloat16*)out, rows, n, write_back);
+    else
+        return AIRUN_ERR_UNSUPPORTED;
+    return airun_launch_status();
+}
+
+// x[t] += delta[t] + vec for every row t (delta and vec may each be absent), and a += b elementwise
+// (vec == nullptr, delta = b): the plain forms of adds that norms otherwise carry out on the way.
+__global__ void add_rows_kernel(float* __restrict__ x, const float* __restrict__ delta, const float* __restrict__ vec,
+                                long long total, int n) {
+    pdl_trigger();
+    pdl_wait();
+    const long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x;
+    if (i >= total) return;
+    float v = x[i];
+    if (delta) v += delta[i];
+    if (vec) v += vec[i % n];
+    x[i] = v;
+}
+
+AIRUN_EXPORT int airun_add_rows(float* x, const float* delta, const float* vec, int T, int n, cudaStream_t stream) {
+    if (T < 0 || n <= 0) return AIRUN_ERR_ARG;
+    const long long total = (long long)T * n;
+    if (total == 0 || (!delta && !vec)) return AIRUN_OK;
+    airun_launch(add_rows_kernel, dim3(ceil_div_i(total, 256)), dim3(256), 0, stream, x, delta, vec, total, n);
+    return airun_launch_status();
+}
+
+// Gated unit with clamped factors: g = min(gate, limit), u = clamp(up, -limit, limit),
+// out = g * sigmoid(slope * g) * (u + 1).  Gate and up columns alternate in blocks of `group` (as for
+// SwiGLU above); the output rows may be strided (a slice of a wider activation buffer).
+template <typename TIn, typename TOut>
+__global__ void glu_clamped_kernel(const TIn* __restrict__ in, TOut* __restrict__ out, long long total, int I, int group,
+                                   long long out_stride, float limit, float slope) {
+    pdl_trigger();
+    pdl_wait();
+    const long long idx = (long long)blockIdx.x * blockDim.x + threadIdx.x;
+    if (idx >= total) return;
+    const long long t = idx / I;
+    const int i = (int)(idx - t * I);
+    const int blk = i / group, o = i - blk * group;
+    const TIn* row = in + t * 2 * (long long)I;
+    const float g = fminf(to_f32<TIn>(row[(size_t)(2 * blk) * group + o]), limit);
+    const float u = fminf(fmaxf(to_f32<TIn>(row[(size_t)(2 * blk + 1) * group + o]), -limit), limit);
+    out[t * out_stride + i] = from_f32<TOut>(g / (1.0f + expf(-slope * g)) * (u + 1.0f));
+}
+
+AIRUN_EXPORT int airun_glu_clamped(const void* in, int in_dtype, void* out, int out_dtype, int T, int I, int group,
+                                   long long out_stride, float limit, float slope, cudaStream_t stream) {
+    if (T < 0 || I <= 0 || group <= 0 || I % group != 0 || out_stride < I || !(limit > 0.0f)) return AIRUN_ERR_ARG;
+    const long long total = (long long)T * I;
+    if (total == 0) return AIRUN_OK;
+    const int threads = 256;
+    const int blocks = ceil_div_i(total, threads);
+    if (in_dtype == AIRUN_DT_F32 && out_dtype == AIRUN_DT_F32)
+        airun_launch(glu_clamped_kernel<float, float>, dim3(blocks), dim3(threads), 0, stream, (const float*)in, (float*)out, total, I, group, out_stride, limit, slope);
+    else if (in_dtype == AIRUN_DT_F32 && out_dtype == AIRUN_DT_BF16)
+        airun_launch(glu_clamped_kernel<float, __nv_bfloat16>, dim3(blocks), dim3(threads), 0, stream, (const float*)in, (__nv_bfloat16*)out, total, I, group, out_stride, limit, slope);
+    else
+        return AIRUN_ERR_UNSUPPORTED;
+    return airun_launch_status();
+}

@@ -1,0 +1,192 @@
+// Gated linear attention: a matrix-valued state per head that decays channel by channel.
+//
+// Per head, with key channels d < D and value channels j < Dv, for the tokens of a request in order:
+//     S[d][j] <- a_t[d] * S[d][j] + k_t[d] * v_t[j]          o_t[j] = sum_d S[d][j] * q_t[d] * q_scale
+// (the output uses the state AFTER the token's own update).  The decay a_t[d] lies in (0, 1):
+//     a_t = sigmoid(z_t)^(1/tau),  z_t = W2 (low_t) + bias,   low_t = the low-rank projection of the input,
+// kept as its logarithm  log a = logsigmoid(z) / tau  (log_decay_kernel), which is what a chunked form sums.
+// Then, per head, o_t is divided by its root mean square over Dv (eps inside the root), multiplied by a
+// weight vector shared by the heads and by silu of a gate projection (out_gate_kernel).
+//
+// State, decays, the recurrence and the norm are float32 whatever the storage of the activations.  The
+// state of a request lives in its slot of the state tensor between steps, stored per head as [Dv][D]
+// (the key channels of one value column side by side), and is zero when the request starts.  The result
+// at a token depends only on the request's tokens up to it, not on how they were cut into steps or on
+// what else is in the batch: the recurrence runs token by token in every case.
+#include "common.cuh"
+
+// log a[t][c] = logsigmoid(bias[c] + sum_j low[t][j] * w2[c][j]) / tau for c < n (= heads * D).
+template <typename TW>
+__global__ void log_decay_kernel(const float* __restrict__ low, long long low_stride, const TW* __restrict__ w2,
+                                 const float* __restrict__ bias, float* __restrict__ out, int n, int rank,
+                                 float inv_tau, const int32_t* __restrict__ req_of_token) {
+    pdl_trigger();
+    pdl_wait();
+    extern __shared__ float s_low[];
+    const int t = blockIdx.x;
+    if (req_of_token[t] < 0) return;
+    for (int j = threadIdx.x; j < rank; j += blockDim.x) s_low[j] = low[(size_t)t * low_stride + j];
+    __syncthreads();
+    for (int c = threadIdx.x; c < n; c += blockDim.x) {
+        float z = bias ? bias[c] : 0.0f;
+        const TW* wr = w2 + (size_t)c * rank;
+        for (int j = 0; j < rank; ++j) z = fmaf(s_low[j], to_f32<TW>(wr[j]), z);
+        // logsigmoid(z) = min(z, 0) - log(1 + exp(-|z|))
+        const float ls = fminf(z, 0.0f) - log1pf(expf(-fabsf(z)));
+        out[(size_t)t * n + c] = ls * inv_tau;
+    }
+}
+
+AIRUN_EXPORT int airun_gla_log_decay(const float* low, long long low_stride, const void* w2, int w_dtype, const float* bias,
+                                     float* out, int T, int n, int rank, float tau, const int32_t* req_of_token,
+                                     cudaStream_t stream) {
+    if (T < 0 || n <= 0 || rank <= 0 || rank > 8192 || !(tau > 0.0f) || !req_of_token) return AIRUN_ERR_ARG;
+    if (T == 0) return AIRUN_OK;
+    const size_t smem = (size_t)rank * sizeof(float);
+    if (w_dtype == AIRUN_DT_F32)
+        airun_launch(log_decay_kernel<float>, dim3(T), dim3(128), smem, stream, low, low_stride, (const float*)w2, bias, out, n, rank, 1.0f / tau, req_of_token);
+    else if (w_dtype == AIRUN_DT_BF16)
+        airun_launch(log_decay_kernel<__nv_bfloat16>, dim3(T), dim3(128), smem, stream, low, low_stride, (const __nv_bfloat16*)w2, bias, out, n, rank, 1.0f / tau, req_of_token);
+    else
+        return AIRUN_ERR_UNSUPPORTED;
+    return airun_launch_status();
+}
+
+// The recurrence.  One block per (request, head, 32 value columns), 256 threads: a warp owns four
+// columns, and the eight lanes of a column own the key channels d = i * 8 + part (i < NS), so a thread
+// keeps NS elements of the state in registers for the whole step.  The tokens of the request are
+// staged through shared memory a few at a time (q, k, exp(log a) per key channel, v per column), each
+// thread updates its strip and the eight partial sums of a column are added by shuffles.
+#define GLA_COLS 32
+template <int NS>
+__global__ __launch_bounds__(256) void gla_recurrent_kernel(
+    const float* __restrict__ q, const float* __restrict__ k, const float* __restrict__ v, long long row_stride,
+    const float* __restrict__ log_decay, float* __restrict__ state, long long slot_stride,
+    const int32_t* __restrict__ cu_tokens, const int32_t* __restrict__ state_slots, int max_slots,
+    float* __restrict__ out, int heads, int D, int Dv, float q_scale, int* __restrict__ err) {
+    pdl_trigger();
+    pdl_wait();
+    constexpr int DP = NS * 8;
+    constexpr int GLA_TT = NS >= 32 ? 8 : 16;        // tokens staged at a time (static shared memory stays under 48 KB)
+    __shared__ float s_q[GLA_TT][DP], s_k[GLA_TT][DP], s_a[GLA_TT][DP], s_v[GLA_TT][GLA_COLS];
+    const int r = blockIdx.x, head = blockIdx.y, col0 = blockIdx.z * GLA_COLS;
+    const int t0 = cu_tokens[r], n = cu_tokens[r + 1] - t0;
+    if (n <= 0) return;
+    const int slot = state_slots[r];
+    if (slot < 0 || slot >= max_slots) {
+        if (threadIdx.x == 0) atomicOr(err, AIRUN_DEV_BAD_REQ);
+        return;
+    }
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+    const int part = lane & 7, cw = warp * 4 + (lane >> 3), col = col0 + cw;
+    const bool col_ok = col < Dv;
+    float* srow = state + (size_t)slot * slot_stride + ((size_t)head * Dv + (col_ok ? col : 0)) * D;
+    float S[NS];
+#pragma unroll
+    for (int i = 0; i < NS; ++i) {
+        const int d = i * 8 + part;
+        S[i] = (col_ok && d < D) ? srow[d] : 0.0f;
+    }
+    for (int base = 0; base < n; base += GLA_TT) {
+        const int nt = min(GLA_TT, n - base);
+        __syncthreads();
+        for (int e = threadIdx.x; e < nt * DP; e += 256) {
+            const int tt = e / DP, d = e - tt * DP;
+            const size_t row = (size_t)(t0 + base + tt);
+            float qv = 0.0f, kv = 0.0f, av = 0.0f;
+            if (d < D) {
+                qv = q[row * row_stride + (size_t)head * D + d];
+                kv = k[row * row_stride + (size_t)head * D + d];
+                av = expf(log_decay[row * ((size_t)heads * D) + (size_t)head * D + d]);
+            }
+            s_q[tt][d] = qv; s_k[tt][d] = kv; s_a[tt][d] = av;
+        }
+        for (int e = threadIdx.x; e < nt * GLA_COLS; e += 256) {
+            const int tt = e / GLA_COLS, c = e - tt * GLA_COLS;
+            s_v[tt][c] = (col0 + c < Dv) ? v[(size_t)(t0 + base + tt) * row_stride + (size_t)head * Dv + col0 + c] : 0.0f;
+        }
+        __syncthreads();
+        for (int tt = 0; tt < nt; ++tt) {
+            const float vj = s_v[tt][cw];
+            float acc = 0.0f;
+#pragma unroll
+            for (int i = 0; i < NS; ++i) {
+                const int d = i * 8 + part;
+                S[i] = fmaf(s_a[tt][d], S[i], s_k[tt][d] * vj);
+                acc = fmaf(S[i], s_q[tt][d], acc);
+            }
+            acc += __shfl_xor_sync(0xffffffffu, acc, 1);
+            acc += __shfl_xor_sync(0xffffffffu, acc, 2);
+            acc += __shfl_xor_sync(0xffffffffu, acc, 4);
+            if (part == 0 && col_ok) out[(size_t)(t0 + base + tt) * ((size_t)heads * Dv) + (size_t)head * Dv + col] = acc * q_scale;
+        }
+    }
+    if (col_ok) {
+#pragma unroll
+        for (int i = 0; i < NS; ++i) {
+            const int d = i * 8 + part;
+            if (d < D) srow[d] = S[i];
+        }
+    }
+}
+
+AIRUN_EXPORT int airun_gla_recurrent(const float* q, const float* k, const float* v, long long row_stride,
+                                     const float* log_decay, float* state, long long slot_stride, int max_slots,
+                                     const int32_t* cu_tokens, const int32_t* state_slots, int num_reqs,
+                                     float* out, int heads, int D, int Dv, float q_scale, int* err, cudaStream_t stream) {
+    if (num_reqs < 0 || heads <= 0 || D <= 0 || D > 256 || Dv <= 0 || !state || !cu_tokens || !state_slots || !err ||
+        slot_stride < (long long)heads * D * Dv || heads > 65535)
+        return AIRUN_ERR_ARG;
+    if (num_reqs == 0) return AIRUN_OK;
+    const int tiles = ceil_div_i(Dv, GLA_COLS);
+    if (tiles > 65535) return AIRUN_ERR_ARG;
+    dim3 grid(num_reqs, heads, tiles);
+#define GLA_LAUNCH(NS) airun_launch(gla_recurrent_kernel<NS>, grid, dim3(256), 0, stream, q, k, v, row_stride, log_decay, state, \
+        slot_stride, cu_tokens, state_slots, max_slots, out, heads, D, Dv, q_scale, err)
+    if (D <= 32) GLA_LAUNCH(4);
+    else if (D <= 64) GLA_LAUNCH(8);
+    else if (D <= 128) GLA_LAUNCH(16);
+    else GLA_LAUNCH(32);
+#undef GLA_LAUNCH
+    return airun_launch_status();
+}
+
+// out[t][h][j] = o[t][h][j] / sqrt(mean_j o^2 + eps) * w[j] * silu(gate[t][h][j]); one warp per (token, head).
+template <typename TOut>
+__global__ __launch_bounds__(128) void out_gate_kernel(const float* __restrict__ o, const float* __restrict__ gate,
+                                                       long long gate_stride, const float* __restrict__ w,
+                                                       TOut* __restrict__ out, long long out_stride, int T, int heads,
+                                                       int Dv, float eps, const int32_t* __restrict__ req_of_token) {
+    pdl_trigger();
+    pdl_wait();
+    const int unit = blockIdx.x * 4 + (threadIdx.x >> 5), lane = threadIdx.x & 31;
+    if (unit >= T * heads) return;
+    const int t = unit / heads, h = unit - t * heads;
+    if (req_of_token[t] < 0) return;
+    const float* orow = o + ((size_t)t * heads + h) * Dv;
+    float ss = 0.0f;
+    for (int j = lane; j < Dv; j += 32) ss = fmaf(orow[j], orow[j], ss);
+    ss = warp_sum(ss);
+    const float inv = 1.0f / sqrtf(ss / (float)Dv + eps);
+    const float* grow = gate + (size_t)t * gate_stride + (size_t)h * Dv;
+    TOut* dst = out + (size_t)t * out_stride + (size_t)h * Dv;
+    for (int j = lane; j < Dv; j += 32) {
+        const float g = grow[j];
+        dst[j] = from_f32<TOut>(orow[j] * inv * (w ? w[j] : 1.0f) * (g / (1.0f + expf(-g))));
+    }
+}
+
+AIRUN_EXPORT int airun_gla_out_gate(const float* o, const float* gate, long long gate_stride, const float* w, void* out,
+                                    int out_dtype, long long out_stride, int T, int heads, int Dv, float eps,
+                                    const int32_t* req_of_token, cudaStream_t stream) {
+    if (T < 0 || heads <= 0 || Dv <= 0 || !req_of_token || out_stride < (long long)heads * Dv) return AIRUN_ERR_ARG;
+    if (T == 0) return AIRUN_OK;
+    const int blocks = ceil_div_i((long long)T * heads, 4);
+    if (out_dtype == AIRUN_DT_F32)
+        airun_launch(out_gate_kernel<float>, dim3(blocks), dim3(128), 0, stream, o, gate, gate_stride, w, (float*)out, out_stride, T, heads, Dv, eps, req_of_token);
+    else if (out_dtype == AIRUN_DT_BF16)
+        airun_launch(out_gate_kernel<__nv_bfloat16>, dim3(blocks), dim3(128), 0, stream, o, gate, gate_stride, w, (__nv_bfloat16*)out, out_stride, T, heads, Dv, eps, req_of_token);
+    else
+        return AIRUN_ERR_UNSUPPORTED;
+    return airun_launch_status();
+}

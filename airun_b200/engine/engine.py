@@ -21,7 +21,7 @@ import numpy as np
 import torch
 
 from ..cache.manager import CacheManager, CacheStorage
-from ..config.base import ModelConfig, architecture_name, lookup_architecture, read_config_json
+from ..config.base import ModelConfig, architecture_name, load_config, lookup_architecture, read_config_json
 from ..kernels import ops
 from ..sampling.sampler import SamplingParams, sample_candidates, sample_rows
 from ..weights.loader import open_model_folder
@@ -124,7 +124,7 @@ class Engine:
         from ..parts.base import PagedKVSpec, StateSpec
         dt = _DTYPES[o.dtype]
         esz = 2 if dt == torch.bfloat16 else 4
-        per_token = sum(2 * s.num_kv_heads * s.head_dim * esz
+        per_token = sum(s.elements_per_token() * esz
                         for s, src in zip(specs, cache_from) if isinstance(s, PagedKVSpec) and src is None)
         if per_token == 0:
             return o.page_size
@@ -144,11 +144,11 @@ class Engine:
         options = options or EngineOptions(**kw)
         cls._require_gpu(options)
         d = read_config_json(model_dir)
-        config_cls, builder = lookup_architecture(architecture_name(d))
-        config = config_cls.from_dict(d)
-        model = builder(config, _DTYPES[options.dtype], options.device)
+        _, builder = lookup_architecture(architecture_name(d))
         src = open_model_folder(model_dir)
         try:
+            config = load_config(model_dir, {n: tuple(src.info(n)[1]) for n in src.names()})
+            model = builder(config, _DTYPES[options.dtype], options.device)
             model.load(src)
         finally:
             src.close()

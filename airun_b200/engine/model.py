@@ -18,7 +18,7 @@ from typing import Dict, List, Optional, Tuple
 import torch
 
 from ..config.base import LayerCall, ModelConfig
-from ..parts.base import make_part
+from ..parts.base import make_part, part_factory
 from ..parts import embedding as _embedding_parts      # noqa: F401  (registers the embedding and head parts)
 from ..weights.loader import (DictSource, TensorSource, WeightSpec, load_tensors, random_tensors)
 
@@ -49,15 +49,28 @@ class DecoderModel:
             p = names["layer"].format(i=i)
             common = dict(dtype=dtype, device=self.device)
             norm1 = make_part("norm", spec.norm, prefix=f"{p}.{names['norm1']}", **spec.norm_args, **common)
-            norm2 = make_part("norm", spec.norm, prefix=f"{p}.{names['norm2']}", **spec.norm_args, **common)
+            # an arrangement with one norm (``num_norms = 1``) gets no second one; a layer without a
+            # feed-forward names none (``feed_forward`` empty)
+            two_norms = getattr(part_factory("arrangement", spec.arrangement), "num_norms", 2) >= 2
+            norm2 = make_part("norm", spec.norm, prefix=f"{p}.{names['norm2']}", **spec.norm_args, **common) \
+                if two_norms else None
             mixer = make_part("mixer", spec.mixer, prefix=f"{p}.{names['mixer']}", **spec.mixer_args, **common)
-            ffn = make_part("feed_forward", spec.feed_forward, prefix=f"{p}.{names['ffn']}", **spec.ffn_args, **common)
+            ffn = make_part("feed_forward", spec.feed_forward, prefix=f"{p}.{names['ffn']}", **spec.ffn_args, **common) \
+                if spec.feed_forward else None
             self.layers.append(make_part("arrangement", spec.arrangement, norm1=norm1, mixer=mixer,
                                          norm2=norm2, ffn=ffn, dtype=dtype))
         self.order: List[LayerCall] = list(config.execution_order())
         for c in self.order:
             if not (0 <= c.layer < len(self.layers)):
                 raise ValueError(f"the execution order names layer {c.layer}, the model has {len(self.layers)}")
+        # the table whose rows entries of the order add to the residual stream before they run (float32 [rows, H])
+        table = config.order_table() if hasattr(config, "order_table") else None
+        self.order_table_name, self.order_table_rows = table if table else (None, 0)
+        self.order_table: Optional[torch.Tensor] = None
+        for c in self.order:
+            if getattr(c, "add_row", None) is not None and not (0 <= c.add_row < self.order_table_rows):
+                raise ValueError(f"the execution order adds row {c.add_row} of a table of {self.order_table_rows} rows")
+        self.layer_hook = None      # debugging and tests: called as hook(entry, residual [T, H]) after every entry
         fn_name, fn_args = config.final_norm() if hasattr(config, "final_norm") else \
             ("rmsnorm", dict(size=H, eps=config.rms_norm_eps))
         self.final_norm = make_part("norm", fn_name, prefix=names["final_norm"], dtype=dtype,
@@ -73,7 +86,10 @@ class DecoderModel:
         return [self.embedding] + self.layers + [self.final_norm, self.head]
 
     def weight_specs(self) -> List[WeightSpec]:
-        return [s for p in self.parts() for s in p.weight_specs()]
+        specs = [s for p in self.parts() for s in p.weight_specs()]
+        if self.order_table_name:
+            specs.append(WeightSpec(self.order_table_name, (self.order_table_rows, self.H), storage="float32"))
+        return specs
 
     def ignorable_tensors(self) -> List[str]:
         # a tied model's file may still carry the head; it is the same matrix
@@ -83,6 +99,8 @@ class DecoderModel:
         tensors = load_tensors(self.weight_specs(), source, self.dtype, self.device, self.ignorable_tensors())
         for p in self.parts():
             p.load_weights(tensors)
+        if self.order_table_name:
+            self.order_table = tensors[self.order_table_name]
         del tensors
         if self.device.type == "cuda":
             self.pack_weights()
@@ -125,6 +143,8 @@ class DecoderModel:
 
         for p in self.parts():
             walk(p)
+        if self.order_table is not None:
+            slots.append((self, "order_table", self.order_table))
         if not slots:
             return
         storages = {}                                        # storage address -> (bytes, offset in the arena)
@@ -190,10 +210,20 @@ class DecoderModel:
             ctx.ws.reset()
             nxt = self.layers[self.order[ci + 1].layer] if ci + 1 < len(self.order) else None
             next_norm = nxt.norm1 if (nxt is not None and getattr(nxt, "accepts_normed", lambda: False)()) else None
+            layer, extra = self.layers[call.layer], {}
+            if getattr(call, "add_row", None) is not None:
+                vec = self.order_table[call.add_row]
+                if getattr(layer, "accepts_add_vec", False):
+                    extra["add_vec"] = vec
+                else:                                   # x += what is pending + the row, by a kernel of its own
+                    from ..kernels import ops
+                    ops.add_rows(x[:T], delta=delta if isinstance(delta, torch.Tensor) else None, vec=vec)
+                    delta = None if isinstance(delta, torch.Tensor) else delta
             if next_norm is not None:
-                delta = self.layers[call.layer].forward(ctx, x, delta, ctx.caches[ci], next_norm=next_norm)
-            else:
-                delta = self.layers[call.layer].forward(ctx, x, delta, ctx.caches[ci])
+                extra["next_norm"] = next_norm
+            delta = layer.forward(ctx, x, delta, ctx.caches[ci], **extra)
+            if self.layer_hook is not None and isinstance(delta, torch.Tensor) and not torch.cuda.is_current_stream_capturing():
+                self.layer_hook(ci, x[:T] + delta[:T])
             if trace:           # synchronises after every block: a debugging aid, as the reference's AIRUN_TRACE_LAYERS
                 r = x[:ctx.num_tokens] if not isinstance(delta, torch.Tensor) else (x[:ctx.num_tokens] + delta[:ctx.num_tokens])
                 print(f"[airun_b200] entry {ci} layer {call.layer}: rms {float(r.pow(2).mean().sqrt()):.6f} "

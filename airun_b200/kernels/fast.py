@@ -517,3 +517,15 @@ def _shared_prefix_slices(n_rows: int, nkv: int, G: int, hd: int, splits: int = 
     want = max(1, min(37, slots // max(1, nkv * groups)))
     room = SCRATCH_FLOATS // (n_rows * nkv * ((G + 15) // 16) * 16 * (hd + 2)) - splits
     return max(0, min(want, room, 64 - splits))
+
+
+# ---------------------------------------------------------------- parts of other designs
+def linear_glu_clamped_bf16(ctx, x: torch.Tensor, w_gu: torch.Tensor, out: torch.Tensor, group: int,
+                            limit: float, slope: float) -> bool:
+    """gate/up product with the clamped gated unit in the epilogue; False: the caller runs product and unit apart."""
+    return False
+
+
+def diff_attention_bf16(ctx, q, out, cache, part) -> bool:
+    """Differential attention on the tensor cores; False: the caller runs the plain kernel."""
+    return False

@@ -88,7 +88,7 @@ def _fn(lib_name: str, fn_name: str, argtypes, defines=None):
 def required_libraries(dtype: torch.dtype, head_dim: int):
     """(name, defines) of every library a model of this dtype and head size uses."""
     libs = [("elementwise", None), ("gemm_simt", None), ("qkv_post", None),
-            ("attention_generic", None), ("sampling", None)]
+            ("attention_generic", None), ("sampling", None), ("linear_attention", None), ("diff_attention", None)]
     return libs
 
 
@@ -180,6 +180,197 @@ def gather_rows(src: torch.Tensor, rows: torch.Tensor, out: torch.Tensor) -> Non
     _need(out.shape[0] >= rows.shape[0] and out.shape[1] == src.shape[1], "gather output too small")
     f = _fn("elementwise", "airun_gather_rows", [c_void_p, c_void_p, c_void_p, c_int, c_int, c_void_p])
     _check(f(_p(src), _p(out), _p(rows), rows.shape[0], rb, _stream()), "gather_rows")
+
+
+def dyt_norm(x: torch.Tensor, alpha: torch.Tensor, weight: torch.Tensor, bias: torch.Tensor, out: torch.Tensor,
+             delta: Optional[torch.Tensor] = None, rows: Optional[torch.Tensor] = None,
+             add_vec: Optional[torch.Tensor] = None) -> None:
+    """out = tanh(alpha * v) * weight + bias with v = x [+ delta] [+ add_vec] (``add_vec``: one row [n] added
+    to every token).  With ``delta`` or ``add_vec`` and no ``rows`` the sum is written back into ``x``; with
+    ``rows`` only those rows are normed, into out[0..len(rows)), and ``x`` is left as it is."""
+    _cuda(x, alpha, weight, bias, out, delta, rows, add_vec)
+    _need(x.dtype == torch.float32 and x.dim() == 2 and x.is_contiguous(), "x must be float32 [T, n]")
+    n = x.shape[1]
+    for w in (weight, bias):
+        _need(w.dtype == torch.float32 and tuple(w.shape) == (n,) and w.is_contiguous(), "norm weight and bias must be float32 [n]")
+    _need(alpha.dtype == torch.float32 and alpha.numel() == 1, "alpha must be one float32 number")
+    if delta is not None:
+        _need(delta.dtype == torch.float32 and delta.shape == x.shape and delta.is_contiguous(), "delta must match x")
+    if add_vec is not None:
+        _need(add_vec.dtype == torch.float32 and tuple(add_vec.shape) == (n,) and add_vec.is_contiguous(),
+              "add_vec must be float32 [n]")
+    n_rows = x.shape[0]
+    if rows is not None:
+        _need(rows.dtype == torch.int32 and rows.dim() == 1 and rows.is_contiguous(), "rows must be int32 [R]")
+        n_rows = rows.shape[0]
+    _need(out.dim() == 2 and out.shape[0] >= n_rows and out.shape[1] == n and out.is_contiguous(),
+          "norm output must be [rows, n]")
+    f = _fn("elementwise", "airun_dyt_norm",
+            [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_void_p, c_int, c_int, c_int,
+             c_void_p])
+    write_back = 1 if ((delta is not None or add_vec is not None) and rows is None) else 0
+    _check(f(_p(x), _p(delta), _p(add_vec), _p(alpha), _p(weight), _p(bias), _p(out), _dt(out), _p(rows), n_rows, n,
+             write_back, _stream()), "dyt_norm")
+
+
+def add_rows(x: torch.Tensor, delta: Optional[torch.Tensor] = None, vec: Optional[torch.Tensor] = None) -> None:
+    """x += delta (same shape) and/or x[t] += vec for every row t, in place, float32."""
+    _cuda(x, delta, vec)
+    _need(x.dtype == torch.float32 and x.dim() == 2 and x.is_contiguous(), "x must be contiguous float32 [T, n]")
+    if delta is not None:
+        _need(delta.dtype == torch.float32 and delta.shape == x.shape and delta.is_contiguous(), "delta must match x")
+    if vec is not None:
+        _need(vec.dtype == torch.float32 and tuple(vec.shape) == (x.shape[1],) and vec.is_contiguous(), "vec must be float32 [n]")
+    f = _fn("elementwise", "airun_add_rows", [c_void_p, c_void_p, c_void_p, c_int, c_int, c_void_p])
+    _check(f(_p(x), _p(delta), _p(vec), x.shape[0], x.shape[1], _stream()), "add_rows")
+
+
+def glu_clamped(gate_up: torch.Tensor, out: torch.Tensor, group: int, limit: float, slope: float) -> None:
+    """out[t, i] = g * sigmoid(slope * g) * (u + 1) with g = min(gate, limit), u = clamp(up, -limit, limit); gate and
+    up columns alternate in blocks of ``group``.  ``out`` may be a column slice of a wider buffer."""
+    _cuda(gate_up, out)
+    _need(gate_up.dim() == 2 and out.dim() == 2 and gate_up.is_contiguous() and out.stride(1) == 1
+          and gate_up.dtype == torch.float32, "glu_clamped takes contiguous float32 [T, 2I] and row-major [T, I]")
+    T, I = out.shape
+    _need(gate_up.shape[0] == T and gate_up.shape[1] == 2 * I, "glu_clamped input must be [T, 2I]")
+    f = _fn("elementwise", "airun_glu_clamped",
+            [c_void_p, c_int, c_void_p, c_int, c_int, c_int, c_int, c_longlong, c_float, c_float, c_void_p])
+    _check(f(_p(gate_up), _dt(gate_up), _p(out), _dt(out), T, I, int(group), out.stride(0) if T > 1 else max(I, out.stride(0)),
+             float(limit), float(slope), _stream()), "glu_clamped")
+
+
+# ---------------------------------------------------------------- gated linear attention
+def _rows_f32(t: torch.Tensor, what: str) -> None:
+    _need(t.dtype == torch.float32 and t.dim() == 2 and t.stride(1) == 1, f"{what} must be float32 rows (a column slice is fine)")
+
+
+def _row_stride(t: torch.Tensor) -> int:
+    return t.stride(0) if t.shape[0] > 1 else max(t.shape[1], t.stride(0))
+
+
+def gla_log_decay(low: torch.Tensor, w2: torch.Tensor, bias: Optional[torch.Tensor], tau: float, out: torch.Tensor,
+                  req_of_token: torch.Tensor) -> None:
+    """out[t, c] = logsigmoid(bias[c] + low[t] . w2[c]) / tau: the logarithm of the decay sigmoid(z)^(1/tau)."""
+    _cuda(low, w2, bias, out, req_of_token)
+    _rows_f32(low, "low")
+    T, rank = low.shape
+    n = w2.shape[0]
+    _need(w2.dim() == 2 and w2.shape[1] == rank and w2.is_contiguous(), "w2 must be contiguous [n, rank]")
+    if bias is not None:
+        _need(bias.dtype == torch.float32 and tuple(bias.shape) == (n,) and bias.is_contiguous(), "bias must be float32 [n]")
+    _need(out.dtype == torch.float32 and tuple(out.shape) == (T, n) and out.is_contiguous(), "out must be float32 [T, n]")
+    _need(req_of_token.dtype == torch.int32 and req_of_token.shape[0] >= T, "req_of_token must be int32 [T]")
+    f = _fn("linear_attention", "airun_gla_log_decay",
+            [c_void_p, c_longlong, c_void_p, c_int, c_void_p, c_void_p, c_int, c_int, c_int, c_float, c_void_p, c_void_p])
+    _check(f(_p(low), _row_stride(low), _p(w2), _dt(w2), _p(bias), _p(out), T, n, rank, float(tau), _p(req_of_token),
+             _stream()), "gla_log_decay")
+
+
+def gla_recurrent(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, log_decay: torch.Tensor, state: torch.Tensor,
+                  cu_tokens: torch.Tensor, state_slots: torch.Tensor, num_reqs: int, out: torch.Tensor,
+                  heads: int, D: int, Dv: int, q_scale: float, err: torch.Tensor) -> None:
+    """The recurrence S <- diag(a) S + k v^T, o = S^T q * q_scale for the tokens of every request in order.
+    ``q``, ``k`` [T, heads*D] and ``v`` [T, heads*Dv] are float32 column slices of ONE buffer (equal row strides);
+    ``state`` is [slots, heads, Dv, D] float32 and is updated in place; ``out`` float32 [T, heads*Dv]."""
+    _cuda(q, k, v, log_decay, state, cu_tokens, state_slots, out, err)
+    for t, w, name in ((q, heads * D, "q"), (k, heads * D, "k"), (v, heads * Dv, "v")):
+        _rows_f32(t, name)
+        _need(t.shape[1] == w, f"{name} must have {w} columns")
+    T = q.shape[0]
+    _need(_row_stride(q) == _row_stride(k) or T <= 1, "q, k and v must share a row stride")
+    _need(k.stride(0) == v.stride(0) or T <= 1, "q, k and v must share a row stride")
+    _need(log_decay.dtype == torch.float32 and tuple(log_decay.shape) == (T, heads * D) and log_decay.is_contiguous(),
+          "log_decay must be float32 [T, heads*D]")
+    _need(state.dtype == torch.float32 and state.dim() == 4 and tuple(state.shape[1:]) == (heads, Dv, D)
+          and state[0].is_contiguous(), "state must be float32 [slots, heads, Dv, D]")
+    _need(out.dtype == torch.float32 and tuple(out.shape) == (T, heads * Dv) and out.is_contiguous(), "out must be float32 [T, heads*Dv]")
+    _need(cu_tokens.dtype == torch.int32 and cu_tokens.numel() >= num_reqs + 1 and state_slots.dtype == torch.int32
+          and state_slots.numel() >= num_reqs, "cu_tokens / state_slots must be int32 [R + 1] / [R]")
+    _need(D <= 256, f"{D} key channels a head are above the kernel's limit of 256")
+    stride = q.stride(0) if T > 1 else max(q.stride(0), k.stride(0), v.stride(0))
+    f = _fn("linear_attention", "airun_gla_recurrent",
+            [c_void_p, c_void_p, c_void_p, c_longlong, c_void_p, c_void_p, c_longlong, c_int, c_void_p, c_void_p, c_int,
+             c_void_p, c_int, c_int, c_int, c_float, c_void_p, c_void_p])
+    _check(f(_p(q), _p(k), _p(v), stride, _p(log_decay), _p(state), state.stride(0), state.shape[0], _p(cu_tokens),
+             _p(state_slots), int(num_reqs), _p(out), heads, D, Dv, float(q_scale), _p(err), _stream()), "gla_recurrent")
+
+
+def gla_out_gate(o: torch.Tensor, gate: torch.Tensor, weight: Optional[torch.Tensor], eps: float, out: torch.Tensor,
+                 heads: int, Dv: int, req_of_token: torch.Tensor) -> None:
+    """out[t, h] = o[t, h] / rms(o[t, h]) * weight * silu(gate[t, h]) per head of ``Dv`` values."""
+    _cuda(o, gate, weight, out, req_of_token)
+    T = o.shape[0]
+    _need(o.dtype == torch.float32 and tuple(o.shape) == (T, heads * Dv) and o.is_contiguous(), "o must be float32 [T, heads*Dv]")
+    _rows_f32(gate, "gate")
+    _need(tuple(gate.shape) == (T, heads * Dv), "gate must be [T, heads*Dv]")
+    _need(out.dim() == 2 and tuple(out.shape) == (T, heads * Dv) and out.stride(1) == 1, "out must be row-major [T, heads*Dv]")
+    if weight is not None:
+        _need(weight.dtype == torch.float32 and tuple(weight.shape) == (Dv,) and weight.is_contiguous(), "weight must be float32 [Dv]")
+    f = _fn("linear_attention", "airun_gla_out_gate",
+            [c_void_p, c_void_p, c_longlong, c_void_p, c_void_p, c_int, c_longlong, c_int, c_int, c_int, c_float, c_void_p,
+             c_void_p])
+    _check(f(_p(o), _p(gate), _row_stride(gate), _p(weight), _p(out), _dt(out), _row_stride(out), T, heads, Dv, float(eps),
+             _p(req_of_token), _stream()), "gla_out_gate")
+
+
+# ---------------------------------------------------------------- differential attention
+def _page_args(pool: torch.Tensor, nkv: int, kd: int, vd: int, page_size: int):
+    _need(pool.is_contiguous() and pool.dim() >= 2 and pool[0].numel() == nkv * page_size * (kd + vd),
+          f"a cache page must hold {nkv} x {page_size} keys of {kd} and values of {vd}")
+    return pool.shape[0]
+
+
+def qkv_bias_store(proj: torch.Tensor, q_bias, k_bias, v_bias, q_out: torch.Tensor, pool: Optional[torch.Tensor],
+                   block_table: Optional[torch.Tensor], positions: torch.Tensor, req_of_token: torch.Tensor,
+                   num_reqs: int, page_size: int, q_width: int, nkv: int, kd: int, vd: int, err: torch.Tensor,
+                   store: bool = True) -> None:
+    """q_out = proj[:, :q_width] + q_bias; the keys (next nkv*kd columns) and values (nkv*vd columns after them) with
+    their biases go into the token's cache page (keys of all KV heads, then values)."""
+    _cuda(proj, q_bias, k_bias, v_bias, q_out, pool, block_table, positions, req_of_token, err)
+    _rows_f32(proj, "proj")
+    T = proj.shape[0]
+    _need(proj.shape[1] >= q_width + (nkv * (kd + vd) if store else 0), "proj is too narrow for q, k and v")
+    _need(tuple(q_out.shape) == (T, q_width) and q_out.is_contiguous(), "q_out must be contiguous [T, q_width]")
+    for b, w in ((q_bias, q_width), (k_bias, nkv * kd), (v_bias, nkv * vd)):
+        if b is not None:
+            _need(b.dtype == torch.float32 and tuple(b.shape) == (w,) and b.is_contiguous(), "a bias must be float32 of its projection's width")
+    num_pages = max_blocks = 0
+    if store:
+        num_pages = _page_args(pool, nkv, kd, vd, page_size)
+        _need(pool.dtype == q_out.dtype, "q and the cache pages must share a type")
+        _need(block_table is not None and block_table.dtype == torch.int32 and block_table.dim() == 2
+              and block_table.stride(1) == 1, "block_table must be int32 [R, max_blocks]")
+        max_blocks = block_table.stride(0)
+    f = _fn("diff_attention", "airun_qkv_bias_store",
+            [c_void_p, c_longlong, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_void_p, c_int, c_void_p,
+             c_void_p, c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_void_p, c_void_p])
+    _check(f(_p(proj), _row_stride(proj), _p(q_bias), _p(k_bias), _p(v_bias), _p(q_out), _p(pool), _dt(q_out),
+             _p(block_table), max_blocks, _p(positions), _p(req_of_token), T, int(num_reqs), num_pages, int(page_size),
+             q_width, nkv, kd, vd, 1 if store else 0, _p(err), _stream()), "qkv_bias_store")
+
+
+def diff_attention(q: torch.Tensor, out: torch.Tensor, pool: torch.Tensor, block_table: torch.Tensor,
+                   positions: torch.Tensor, req_of_token: torch.Tensor, num_reqs: int, page_size: int,
+                   nh: int, nkv: int, D: int, Dv: int, scale: float, cap: float, chunk: int, window: int,
+                   lam: float, eps: float, out_scale: float, err: torch.Tensor) -> None:
+    """Two attention maps per head over the same values, o = a1 - lam * a2, then o / rms(o) * out_scale per head
+    (see csrc/diff_attention.cu); float32 arithmetic, any sizes up to 256."""
+    _cuda(q, out, pool, block_table, positions, req_of_token, err)
+    T = q.shape[0]
+    _need(tuple(q.shape) == (T, nh * 2 * D) and q.is_contiguous(), "q must be contiguous [T, heads*2*D]")
+    _need(tuple(out.shape) == (T, nh * Dv) and out.stride(1) == 1 and out.dtype == q.dtype, "out must be row-major [T, heads*Dv] of q's type")
+    _need(D <= 256 and Dv <= 256, "head sizes above 256 are not taken")
+    _need(nh % nkv == 0, "query heads must be a multiple of KV heads")
+    num_pages = _page_args(pool, nkv, 2 * D, Dv, page_size)
+    _need(pool.dtype == q.dtype, "q and the cache pages must share a type")
+    _need(block_table.dtype == torch.int32 and block_table.dim() == 2 and block_table.stride(1) == 1,
+          "block_table must be int32 [R, max_blocks]")
+    f = _fn("diff_attention", "airun_diff_attention",
+            [c_void_p, c_void_p, c_longlong, c_void_p, c_int, c_void_p, c_int, c_void_p, c_void_p, c_int, c_int, c_int,
+             c_int, c_int, c_int, c_int, c_int, c_float, c_float, c_int, c_int, c_float, c_float, c_float, c_void_p, c_void_p])
+    _check(f(_p(q), _p(out), _row_stride(out), _p(pool), _dt(q), _p(block_table), block_table.stride(0), _p(positions),
+             _p(req_of_token), T, int(num_reqs), num_pages, int(page_size), nh, nkv, D, Dv, float(scale), float(cap),
+             int(chunk), int(window), float(lam), float(eps), float(out_scale), _p(err), _stream()), "diff_attention")
 
 
 # ---------------------------------------------------------------- matrix products

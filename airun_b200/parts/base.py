@@ -23,6 +23,13 @@ Head            forward(ctx, h [rows, hidden], out float32 [rows, vocab])
 Mixer           cache_spec() -> PagedKVSpec | StateSpec | None
                 forward(ctx, h, cache) -> float32 [T, hidden] (the residual delta)
 FeedForward     forward(ctx, h) -> float32 [T, hidden]
+                Optional, for both: the split form, which lets an arrangement run the output products
+                of several sub-layers as ONE product over their concatenated activations:
+                ``core_width`` (columns of the activation its output product reads), ``w_out``
+                ([hidden, core_width], set by load_weights) and ``forward_core(ctx, h, act[, cache])``,
+                which writes the activation into ``act`` (a [T, core_width] view whose rows may be
+                strided) instead of projecting it; after ``adopt_w_out(view)`` the part's own ``w_out``
+                is a view of the arrangement's stacked matrix.
                 Optional, for both: ``fuses_norms = True`` says that forward also takes
                 ``sink=ResidualSink`` (then it adds its result to the residual itself and returns
                 NormedActivations for the next sub-layer, or ignores the sink and returns a delta)
@@ -52,10 +59,21 @@ from ..weights.loader import WeightSpec
 
 @dataclass(frozen=True)
 class PagedKVSpec:
-    """Keys and values of every (or the last ``window``) token(s), in pages."""
+    """Keys and values of every (or the last ``window``) token(s), in pages.  ``head_dim`` is the size of a
+    key row of one KV head; a value row has ``value_dim`` elements when that differs (0: the same).  A page
+    holds the keys of all heads, then the values: [kv_heads, page_size, head_dim] + [kv_heads, page_size,
+    value_dim], which with equal sizes is [2, kv_heads, page_size, head_dim]."""
     num_kv_heads: int
     head_dim: int
     window: int = 0          # 0: all tokens are kept
+    value_dim: int = 0       # 0: values have head_dim elements too
+
+    @property
+    def v_dim(self) -> int:
+        return self.value_dim or self.head_dim
+
+    def elements_per_token(self) -> int:
+        return self.num_kv_heads * (self.head_dim + self.v_dim)
 
 
 @dataclass(frozen=True)
@@ -156,6 +174,13 @@ def register_part(kind: str, name: str, factory: Callable) -> None:
     if kind not in _REGISTRIES:
         raise KeyError(f"unknown kind of part {kind!r}; kinds: {sorted(_REGISTRIES)}")
     _REGISTRIES[kind][name] = factory
+
+
+def part_factory(kind: str, name: str) -> Callable:
+    reg = _REGISTRIES[kind]
+    if name not in reg:
+        raise KeyError(f"no {kind} named {name!r} is registered; registered: {sorted(reg)}")
+    return reg[name]
 
 
 def make_part(kind: str, name: str, **kwargs):

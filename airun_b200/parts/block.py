@@ -79,3 +79,85 @@ class PreNormBlock(Part):
 
 
 register_part("arrangement", "pre_norm", PreNormBlock)
+
+
+class ParallelBlock(Part):
+    """One norm, two sub-layers side by side: h = norm(x), x += mixer(h) + ffn(h).  The feed-forward may be
+    absent.  As with PreNormBlock the add is left to whoever norms x next: the block returns the delta.
+
+    When both sub-layers have the split form (parts/base.py) their output products run as ONE product:
+    each writes its activation into a column slice of one buffer, and that buffer is multiplied by the
+    output matrices set side by side, [Wo | Wdown], which is mixer(h) + ffn(h) with a single accumulation and
+    no add kernel.  Otherwise both run whole and their deltas are added by a kernel.
+
+    ``add_vec`` (float32 [hidden]): a row added to every token of x before the norm, on the norm's way when
+    it can (``takes_add_vec``)."""
+    num_norms = 1
+
+    def __init__(self, norm1: Norm, mixer: Mixer, norm2: Optional[Norm], ffn: Optional[FeedForward], dtype: torch.dtype):
+        self.norm1, self.mixer, self.ffn, self.dtype = norm1, mixer, ffn, dtype
+        self.w_out: Optional[torch.Tensor] = None
+        self.split = all(hasattr(p, "forward_core") and hasattr(p, "adopt_w_out") for p in self.subs())
+
+    def subs(self):
+        return (self.mixer,) if self.ffn is None else (self.mixer, self.ffn)
+
+    def parts(self):
+        return (self.norm1,) + self.subs()
+
+    def weight_specs(self) -> List[WeightSpec]:
+        return [s for p in self.parts() for s in p.weight_specs()]
+
+    def load_weights(self, tensors: Dict[str, torch.Tensor]) -> None:
+        for p in self.parts():
+            p.load_weights(tensors)
+        if self.split and len(self.subs()) > 1:
+            self.w_out = torch.cat([p.w_out for p in self.subs()], dim=1).contiguous()
+            at = 0
+            for p in self.subs():
+                p.adopt_w_out(self.w_out[:, at:at + p.core_width])
+                at += p.core_width
+
+    def cache_spec(self):
+        return self.mixer.cache_spec()
+
+    def device_driven(self) -> bool:
+        return all(getattr(p, "device_driven", False) for p in self.parts())
+
+    def graph_safe(self) -> bool:
+        return all(getattr(p, "graph_safe", True) for p in self.parts())
+
+    def accepts_normed(self) -> bool:
+        return False
+
+    accepts_add_vec = True
+
+    def forward(self, ctx, x: torch.Tensor, pending, cache, next_norm: Optional[Norm] = None, add_vec=None):
+        T, H = x.shape
+        h = ctx.ws.alloc((T, H), self.dtype)
+        if add_vec is not None and not getattr(self.norm1, "takes_add_vec", False):
+            from ..kernels import ops
+            ops.add_rows(x, delta=pending, vec=add_vec)
+            pending, add_vec = None, None
+        if add_vec is not None:
+            self.norm1.forward(ctx, x, h, delta=pending, add_vec=add_vec)
+        else:
+            self.norm1.forward(ctx, x, h, delta=pending)
+        if self.ffn is None:
+            return self.mixer.forward(ctx, h, cache)
+        if self.split:
+            from .linear import linear
+            km = self.mixer.core_width
+            act = ctx.ws.alloc((T, km + self.ffn.core_width), self.dtype)
+            self.mixer.forward_core(ctx, h, act[:, :km], cache)
+            self.ffn.forward_core(ctx, h, act[:, km:])
+            delta = ctx.ws.alloc((T, H), torch.float32)
+            linear(ctx, act, self.w_out, delta)
+            return delta
+        from ..kernels import ops
+        a = self.mixer.forward(ctx, h, cache)
+        ops.add_rows(a, delta=self.ffn.forward(ctx, h))
+        return a
+
+
+register_part("arrangement", "parallel", ParallelBlock)

@@ -70,3 +70,63 @@ class SwiGLU(FeedForward):
 
 
 register_part("feed_forward", "swiglu", SwiGLU)
+
+
+class ClampedGLU(FeedForward):
+    """Gated unit whose factors are clamped: g = min(Wg h, limit), u = clamp(Wu h, -limit, limit),
+    a = g * sigmoid(slope * g) * (u + 1), out = Wd a.  ``slope`` 1.702 makes g * sigmoid(slope * g) the usual
+    sigmoid approximation of GELU.  Gate and up run as one product over rows interleaved in blocks of
+    ``group`` (as in SwiGLU above).  It has the split form (parts/base.py): ``forward_core`` writes ``a`` into
+    a buffer the arrangement gives it and ``w_out`` is Wd."""
+    device_driven = True
+
+    def __init__(self, prefix: str, hidden_size: int, intermediate_size: int, limit: float, slope: float = 1.702,
+                 dtype: torch.dtype = torch.bfloat16, device=None, names: Optional[Dict[str, str]] = None):
+        self.prefix, self.H, self.I = prefix, int(hidden_size), int(intermediate_size)
+        self.limit, self.slope = float(limit), float(slope)
+        if not self.limit > 0:
+            raise ValueError(f"the clamp limit must be positive, found {limit}")
+        self.dtype, self.device = dtype, device
+        self.group = INTERLEAVE if self.I % INTERLEAVE == 0 else self.I
+        n = dict(gate="gate", up="up", down="down")
+        n.update(names or {})
+        self.names = {k: f"{prefix}.{v}" for k, v in n.items()}
+        self.w_gu = self.w_out = None
+        self.core_width = self.I
+
+    def weight_specs(self) -> List[WeightSpec]:
+        nm = self.names
+        return [WeightSpec(nm["gate"], (self.I, self.H)), WeightSpec(nm["up"], (self.I, self.H)),
+                WeightSpec(nm["down"], (self.H, self.I))]
+
+    def load_weights(self, tensors: Dict[str, torch.Tensor]) -> None:
+        nm, g = self.names, self.group
+        gate, up = tensors.pop(nm["gate"]), tensors.pop(nm["up"])
+        nb = self.I // g
+        self.w_gu = torch.stack([gate.view(nb, g, self.H), up.view(nb, g, self.H)], dim=1) \
+            .reshape(2 * self.I, self.H).contiguous()
+        self.w_out = tensors.pop(nm["down"])
+
+    def adopt_w_out(self, view: torch.Tensor) -> None:
+        self.w_out = view
+
+    def forward_core(self, ctx, h: torch.Tensor, act: torch.Tensor) -> None:
+        T = h.shape[0]
+        if h.dtype == torch.bfloat16:
+            from ..kernels import fast
+            if fast.linear_glu_clamped_bf16(ctx, h, self.w_gu, act, self.group, self.limit, self.slope):
+                return
+        gu = ctx.ws.alloc((T, 2 * self.I), torch.float32)
+        linear(ctx, h, self.w_gu, gu)
+        ops.glu_clamped(gu, act, self.group, self.limit, self.slope)
+
+    def forward(self, ctx, h, sink=None):
+        T = h.shape[0]
+        act = ctx.ws.alloc((T, self.I), self.dtype)
+        self.forward_core(ctx, h, act)
+        delta = ctx.ws.alloc((T, self.H), torch.float32)
+        linear(ctx, act, self.w_out, delta)
+        return delta
+
+
+register_part("feed_forward", "clamped_glu", ClampedGLU)
