@@ -155,6 +155,16 @@ __device__ __forceinline__ uint64_t smem_desc_sw128(uint32_t addr) {
 }
 
 __device__ __forceinline__ float silu_mul(float g, float u) { return g / (1.0f + __expf(-g)) * u; }
+// The gated unit of the epilogue.  limit == 0: SwiGLU, silu(g) * u.  limit > 0: the clamped unit,
+// g' = min(g, limit), u' = clamp(u, -limit, limit), g' * sigmoid(slope * g') * (u' + 1).
+__device__ __forceinline__ float gated_unit(float limit, float slope, float g, float u) {
+    if (limit > 0.0f) {
+        g = fminf(g, limit);
+        u = fminf(fmaxf(u, -limit), limit);
+        return g / (1.0f + __expf(-slope * g)) * (u + 1.0f);
+    }
+    return silu_mul(g, u);
+}
 
 struct GemmParams {
     int a_rows, b_rows, K;        // extents of the A and B operands
@@ -179,6 +189,7 @@ struct GemmParams {
     int ssq_out_ld;
     int cluster_reduce;           // the ksplit CTAs of a tile are one cluster and add their slices through
                                   // distributed shared memory instead of the scratch
+    float glu_limit, glu_slope;   // EPI_SWIGLU: 0, 0 for SwiGLU; a limit > 0 for the clamped gated unit
 };
 
 template <int BN, int STAGES>
@@ -244,7 +255,8 @@ __device__ __forceinline__ void store_swiglu_normal(const GemmParams& p, const f
         uint32_t w[8];
 #pragma unroll
         for (int i = 0; i < 8; ++i) {
-            __nv_bfloat162 h = __floats2bfloat162_rn(silu_mul(g[2 * i], u[2 * i]), silu_mul(g[2 * i + 1], u[2 * i + 1]));
+            __nv_bfloat162 h = __floats2bfloat162_rn(gated_unit(p.glu_limit, p.glu_slope, g[2 * i], u[2 * i]),
+                                                      gated_unit(p.glu_limit, p.glu_slope, g[2 * i + 1], u[2 * i + 1]));
             w[i] = *reinterpret_cast<uint32_t*>(&h);
         }
         *reinterpret_cast<uint4*>(o) = make_uint4(w[0], w[1], w[2], w[3]);
@@ -253,7 +265,7 @@ __device__ __forceinline__ void store_swiglu_normal(const GemmParams& p, const f
     }
 #pragma unroll
     for (int i = 0; i < 16; ++i)
-        if (b0 + c0 + 16 + i < p.b_rows) o[i] = __float2bfloat16_rn(silu_mul(g[i], u[i]));
+        if (b0 + c0 + 16 + i < p.b_rows) o[i] = __float2bfloat16_rn(gated_unit(p.glu_limit, p.glu_slope, g[i], u[i]));
 }
 
 // SwiGLU, swapped mode: this lane's row is a gate row when (a_row / 16) is even, and lane + 16
@@ -266,7 +278,7 @@ __device__ __forceinline__ void store_swiglu_swapped(const GemmParams& p, const 
         const int tok = b0 + c0 + i;
         if (lane < 16 && tok < p.b_rows && a_row < p.a_rows) {
             const int n_out = (a_row / 32) * 16 + (a_row % 32);
-            ((__nv_bfloat16*)p.out)[(size_t)tok * p.ldc + n_out] = __float2bfloat16_rn(silu_mul(v[i], up));
+            ((__nv_bfloat16*)p.out)[(size_t)tok * p.ldc + n_out] = __float2bfloat16_rn(gated_unit(p.glu_limit, p.glu_slope, v[i], up));
         }
     }
 }
@@ -949,12 +961,12 @@ AIRUN_EXPORT long long airun_gemm_tcgen05_scratch_floats(int M, int N, int swap,
 // counters: one int per tile, zero on entry when ksplit > 1 (the kernel leaves them zero).
 // ssq_in: when not null, x is an un-normalised bfloat16(resid * norm_w) and every token's results are
 //   multiplied by rsqrt(sum over ssq_parts of ssq_in[part][token] / norm_size + eps).
-AIRUN_EXPORT int airun_gemm_tcgen05_ex(const void* x, const void* W, void* out, int M, int N, int K,
-                                       long long ldx, long long ldw, long long ldc, int epi, int swap, int bn,
-                                       int ksplit, float* scratch, int* counters, int* err, cudaStream_t stream,
-                                       const float* ssq_in, int ssq_parts, int ssq_ld, float eps_in, int norm_size,
-                                       float* resid, long long ld_resid, const float* norm_w, float* ssq_out,
-                                       int ssq_out_ld) {
+static int gemm_launch(const void* x, const void* W, void* out, int M, int N, int K,
+                       long long ldx, long long ldw, long long ldc, int epi, int swap, int bn,
+                       int ksplit, float* scratch, int* counters, int* err, cudaStream_t stream,
+                       const float* ssq_in, int ssq_parts, int ssq_ld, float eps_in, int norm_size,
+                       float* resid, long long ld_resid, const float* norm_w, float* ssq_out,
+                       int ssq_out_ld, float glu_limit, float glu_slope) {
     if (M <= 0 || N <= 0 || K <= 0 || !err) return M == 0 ? AIRUN_OK : AIRUN_ERR_ARG;
     if (K % 8 != 0 || ldx % 8 != 0 || ldw % 8 != 0 || ((uintptr_t)x & 15) || ((uintptr_t)W & 15)) return AIRUN_ERR_ARG;
     if (epi == EPI_SWIGLU && (N % 32 != 0)) return AIRUN_ERR_ARG;
@@ -995,6 +1007,8 @@ AIRUN_EXPORT int airun_gemm_tcgen05_ex(const void* x, const void* W, void* out, 
     p.scratch = scratch;
     p.counters = counters;
     p.err = err;
+    p.glu_limit = glu_limit;
+    p.glu_slope = glu_slope;
     p.ssq_in = ssq_in; p.ssq_parts = ssq_parts; p.ssq_ld = ssq_ld; p.eps_in = eps_in;
     p.inv_n_in = norm_size > 0 ? 1.0f / (float)norm_size : 0.0f;
     p.resid = resid; p.ld_resid = ld_resid; p.norm_w = norm_w; p.ssq_out = ssq_out; p.ssq_out_ld = ssq_out_ld;
@@ -1017,6 +1031,27 @@ AIRUN_EXPORT int airun_gemm_tcgen05_ex(const void* x, const void* W, void* out, 
     if (epi == EPI_RESID) return dispatch<EPI_RESID>(swap != 0, bn, ma, mb, p, grid, stream);
 #endif
     return AIRUN_ERR_UNSUPPORTED;
+}
+
+AIRUN_EXPORT int airun_gemm_tcgen05_ex(const void* x, const void* W, void* out, int M, int N, int K,
+                                       long long ldx, long long ldw, long long ldc, int epi, int swap, int bn,
+                                       int ksplit, float* scratch, int* counters, int* err, cudaStream_t stream,
+                                       const float* ssq_in, int ssq_parts, int ssq_ld, float eps_in, int norm_size,
+                                       float* resid, long long ld_resid, const float* norm_w, float* ssq_out,
+                                       int ssq_out_ld) {
+    return gemm_launch(x, W, out, M, N, K, ldx, ldw, ldc, epi, swap, bn, ksplit, scratch, counters, err, stream, ssq_in,
+                       ssq_parts, ssq_ld, eps_in, norm_size, resid, ld_resid, norm_w, ssq_out, ssq_out_ld, 0.0f, 0.0f);
+}
+
+// The gate/up product with the clamped gated unit in its epilogue (see gated_unit above): the rows of W
+// alternate between blocks of 16 gate and 16 up rows, out is bfloat16 [M, N/2] with row stride ldc.
+AIRUN_EXPORT int airun_gemm_tcgen05_glu(const void* x, const void* W, void* out, int M, int N, int K,
+                                        long long ldx, long long ldw, long long ldc, int swap, int bn, int ksplit,
+                                        float* scratch, int* counters, int* err, cudaStream_t stream, float limit,
+                                        float slope) {
+    if (!(limit > 0.0f)) return AIRUN_ERR_ARG;
+    return gemm_launch(x, W, out, M, N, K, ldx, ldw, ldc, EPI_SWIGLU, swap, bn, ksplit, scratch, counters, err, stream,
+                       nullptr, 0, 0, 0.0f, 0, nullptr, 0, nullptr, nullptr, 0, limit, slope);
 }
 
 AIRUN_EXPORT int airun_gemm_tcgen05(const void* x, const void* W, void* out, int M, int N, int K,

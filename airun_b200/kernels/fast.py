@@ -67,7 +67,7 @@ DISABLED = set(filter(None, os.environ.get("AIRUN_DISABLE_FAST", "").split(","))
 
 def all_libraries():
     return [("gemm_tcgen05", None), ("gemm_tcgen05", {"AIRUN_FOLD_NORM": 1}), ("attention_plan", None), ("attention_mma", {"HD": 128}), ("attention_mma", {"HD": 64}),
-            ("attention_tcgen05", {"HD": 128}), ("attention_tcgen05", {"HD": 64})]
+            ("attention_tcgen05", {"HD": 128}), ("attention_tcgen05", {"HD": 64}), ("diff_attention_mma", None)]
 
 
 def scratch_for(device: torch.device) -> Tuple[torch.Tensor, torch.Tensor]:
@@ -522,10 +522,63 @@ def _shared_prefix_slices(n_rows: int, nkv: int, G: int, hd: int, splits: int = 
 # ---------------------------------------------------------------- parts of other designs
 def linear_glu_clamped_bf16(ctx, x: torch.Tensor, w_gu: torch.Tensor, out: torch.Tensor, group: int,
                             limit: float, slope: float) -> bool:
-    """gate/up product with the clamped gated unit in the epilogue; False: the caller runs product and unit apart."""
-    return False
+    """gate/up product with the clamped gated unit in the epilogue (csrc/gemm_tcgen05.cu: gated_unit); ``out`` may
+    be a column slice of a wider bfloat16 buffer.  False: the caller runs the product and the unit apart."""
+    if group != 16 or not _usable(x, w_gu) or w_gu.shape[0] % 32 != 0 or out.dtype != torch.bfloat16 or out.stride(1) != 1:
+        return False
+    M, K = x.shape
+    N = w_gu.shape[0]
+    _cuda(x, w_gu, out, ctx.err)
+    _need(tuple(out.shape) == (M, N // 2), "the gated unit's epilogue writes bfloat16 [M, N/2]")
+    swap, bn, ksplit = plan_gemm(M, N, K)
+    scratch = counters = None
+    if ksplit > 1:
+        scratch, counters = scratch_for(x.device)
+        f = _fn("gemm_tcgen05", "airun_gemm_tcgen05_scratch_floats", [c_int, c_int, c_int, c_int, c_int])
+        f.restype = c_longlong
+        a_rows, b_rows = (N, M) if swap else (M, N)
+        tiles = ((a_rows + 127) // 128) * ((b_rows + bn - 1) // bn)
+        _need(f(M, N, 1 if swap else 0, bn, ksplit) <= scratch.numel() and tiles <= counters.numel(),
+              "split-K scratch is too small for this launch")
+    f = _fn("gemm_tcgen05", "airun_gemm_tcgen05_glu",
+            [c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_longlong, c_longlong, c_longlong, c_int, c_int, c_int,
+             c_void_p, c_void_p, c_void_p, c_void_p, c_float, c_float])
+    _check(f(_p(x), _p(w_gu), _p(out), M, N, K, x.stride(0) if M > 1 else max(K, x.stride(0)), w_gu.stride(0),
+             out.stride(0) if M > 1 else max(out.shape[1], out.stride(0)), 1 if swap else 0, bn, ksplit,
+             _p(scratch), _p(counters), _p(ctx.err), _stream(), float(limit), float(slope)), "gemm_tcgen05_glu")
+    return True
+
+
+DIFF_TILE_ROWS = 64                    # tokens of one CTA of the tensor-core differential attention
+
+
+def diff_attention_supported(D: int, Dv: int) -> bool:
+    return "diff_attention" not in DISABLED and D <= 128 and Dv <= 128
 
 
 def diff_attention_bf16(ctx, q, out, cache, part) -> bool:
-    """Differential attention on the tensor cores; False: the caller runs the plain kernel."""
-    return False
+    """Differential attention on the tensor cores (csrc/diff_attention_mma.cu) for every row of the batch, prompt
+    portions and single tokens alike; False: the caller runs the plain kernel (head sizes above 128)."""
+    D, Dv, nh, nkv = part.D, part.Dv, part.nh, part.nkv
+    if q.dtype != torch.bfloat16 or cache.pool.dtype != torch.bfloat16 or not diff_attention_supported(D, Dv):
+        return False
+    _cuda(q, out, cache.pool, cache.block_table, ctx.cu_tokens, ctx.context_lens, ctx.err)
+    T = q.shape[0]
+    _need(tuple(q.shape) == (T, nh * 2 * D) and q.is_contiguous(), "q must be contiguous [T, heads*2*D]")
+    _need(tuple(out.shape) == (T, nh * Dv) and out.stride(1) == 1 and out.dtype == torch.bfloat16,
+          "out must be row-major bfloat16 [T, heads*Dv]")
+    pool, bt = cache.pool, cache.block_table
+    _need(pool.is_contiguous() and pool[0].numel() == nkv * cache.page_size * (2 * D + Dv), "the cache pages do not fit the head sizes")
+    _need(ctx.cu_tokens.numel() >= ctx.num_reqs + 1 and ctx.context_lens.numel() >= ctx.num_reqs,
+          "the batch's layout arrays are shorter than its number of requests")
+    # every request's tokens are cut into tiles of 64; the kernel walks cu_tokens to find its tile, so the
+    # launch only needs an upper bound of their number
+    max_tiles = (T + DIFF_TILE_ROWS - 1) // DIFF_TILE_ROWS + int(ctx.num_reqs)
+    f = _fn("diff_attention_mma", "airun_diff_attention_mma",
+            [c_void_p, c_void_p, c_longlong, c_void_p, c_void_p, c_int, c_void_p, c_void_p, c_int, c_int, c_int, c_int,
+             c_int, c_int, c_int, c_int, c_float, c_float, c_int, c_int, c_float, c_float, c_float, c_void_p, c_void_p])
+    _check(f(_p(q), _p(out), out.stride(0) if T > 1 else max(out.shape[1], out.stride(0)), _p(pool), _p(bt), bt.stride(0),
+             _p(ctx.cu_tokens), _p(ctx.context_lens), int(ctx.num_reqs), max_tiles, pool.shape[0], int(cache.page_size),
+             nh, nkv, D, Dv, float(part.scale), float(part.cap), int(part.chunk), int(part.window), float(part.lam),
+             float(part.eps), 1.0 - float(part.lambda_init), _p(ctx.err), _stream()), "diff_attention_mma")
+    return True

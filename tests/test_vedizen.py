@@ -359,6 +359,41 @@ def test_differential_attention_kernel_over_scrambled_pages(heads, kvh, D, Dv, c
         at += b - a
 
 
+def tensor_core_attention(case, lens, new, heads, kvh, D, Dv, scale, cap, lam, chunk, eps, osc):
+    """The batch of ``paged_attention_case`` through the tensor-core kernel; returns [rows, heads*Dv] float64."""
+    from types import SimpleNamespace as NS
+    from airun_b200.kernels import fast
+    rows, spans, q, pos, req = case["last"]
+    counts = [spans[r][1] - spans[r][0] if r in rows else 0 for r in range(len(lens))]
+    ctx = NS(cu_tokens=torch.tensor(np.cumsum([0] + counts), dtype=torch.int32, device="cuda"),
+             context_lens=torch.tensor(lens, dtype=torch.int32, device="cuda"), num_reqs=len(lens), err=case["err"])
+    part = NS(D=D, Dv=Dv, nh=heads, nkv=kvh, scale=scale, cap=cap, chunk=chunk, window=0, lam=lam, eps=eps, lambda_init=1.0 - osc)
+    cache = NS(pool=case["pool"], block_table=case["bt"], page_size=case["page"])
+    out = torch.full((q.shape[0], heads * Dv + 8), 7.0, device="cuda", dtype=torch.bfloat16)
+    assert fast.diff_attention_bf16(ctx, q, out[:, 8:], cache, part)
+    assert (out[:, :8] == 7.0).all()
+    return out[:, 8:].cpu().double()
+
+
+@gpu
+@pytest.mark.parametrize("heads,kvh,D,Dv,chunk,page", [(6, 3, 16, 24, 37, 8), (2, 2, 8, 16, 11, 16), (4, 1, 40, 72, 0, 24),
+                                                         (3, 1, 128, 128, 50, 16), (4, 2, 64, 128, 100, 16), (2, 1, 20, 36, 64, 16)])
+def test_tensor_core_differential_attention_against_the_plain_formula(heads, kvh, D, Dv, chunk, page):
+    lens, new = [150, 9, 77, 1, 64], [150, 1, 5, 1, 64]     # whole prompts (three and one tile), single tokens, a portion
+    scale, cap, lam, eps, osc = D ** -0.5, 6.0, 0.45, 1e-5, 0.7
+    case = paged_attention_case(lens, new, heads, kvh, D, Dv, chunk, page, torch.bfloat16, seed=heads + D)
+    got = tensor_core_attention(case, lens, new, heads, kvh, D, Dv, scale, cap, lam, chunk, eps, osc)
+    assert int(case["err"].item()) == 0
+    rows, spans = case["last"][0], case["last"][1]
+    at = 0
+    for r in rows:
+        a, b = spans[r]
+        want = plain_attention_rows(case, r, heads, kvh, D, Dv, scale, cap, lam, chunk, eps, osc, rnd=P.to_bf16_and_back)[a:b]
+        err = (got[at:at + b - a] - want).abs()
+        assert float(err.max()) < 4e-2 and float(err.mean()) < 4e-3, f"request {r}: {float(err.max())}, {float(err.mean())}"
+        at += b - a
+
+
 @gpu
 @pytest.mark.parametrize("where", ["inside", "outside", "far"])
 def test_one_dominant_key_at_a_chunk_edge(where):
@@ -381,8 +416,11 @@ def test_one_dominant_key_at_a_chunk_edge(where):
         rows, spans, q, pos, req = case["last"]
         out = torch.empty(1, heads * Dv, device="cuda", dtype=dtype)
         # lambda 0: the output of head 0 is its map 1 alone, normed
-        ops.diff_attention(q, out, case["pool"], case["bt"], pos, req, 1, page, heads, kvh, D, Dv, 1.0, 0.0, chunk, 0, 0.0,
-                           1e-6, 1.0, case["err"])
+        if dtype == torch.float32:
+            ops.diff_attention(q, out, case["pool"], case["bt"], pos, req, 1, page, heads, kvh, D, Dv, 1.0, 0.0, chunk, 0, 0.0,
+                               1e-6, 1.0, case["err"])
+        else:
+            out = tensor_core_attention(case, [n], [1], heads, kvh, D, Dv, 1.0, 0.0, 0.0, chunk, 1e-6, 1.0).to(dtype).cuda()
         rnd = None if dtype == torch.float32 else P.to_bf16_and_back
         want = plain_attention_rows(case, 0, heads, kvh, D, Dv, 1.0, 0.0, 0.0, chunk, 1e-6, 1.0, rnd)[-1:]
         tol = 1e-4 if dtype == torch.float32 else 3e-2
