@@ -35,6 +35,12 @@ __device__ __forceinline__ uint32_t pack_bf16(float lo, float hi) {
 // about 1e-7 near it
 __device__ __forceinline__ float tanh_exp(float y) { return 1.0f - __fdividef(2.0f, __expf(2.0f * y) + 1.0f); }
 
+__device__ __forceinline__ void cp_async16(void* smem, const void* gmem) {
+    asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"((uint32_t)__cvta_generic_to_shared(smem)), "l"(gmem) : "memory");
+}
+__device__ __forceinline__ void cp_async_commit() { asm volatile("cp.async.commit_group;" ::: "memory"); }
+template <int N> __device__ __forceinline__ void cp_async_wait() { asm volatile("cp.async.wait_group %0;" ::"n"(N) : "memory"); }
+
 struct DamParams {
     const __nv_bfloat16* q;
     __nv_bfloat16* out;
@@ -47,6 +53,7 @@ struct DamParams {
     int num_reqs, num_pages, page_size, nh, nkv, D, Dv;
     float scale, cap, lambda, eps, out_scale;
     int chunk, window;
+    int skip_single;              // requests that bring ONE token are left to the decode kernel
     int* err;
 };
 
@@ -58,13 +65,14 @@ __global__ __launch_bounds__(128) void diff_attention_mma_kernel(const DamParams
     constexpr int VS = DVP + DAM_PAD;             // row stride of Vs
     extern __shared__ __align__(16) unsigned char dam_smem[];
     __nv_bfloat16* Qs = reinterpret_cast<__nv_bfloat16*>(dam_smem);            // [64][QS]
-    __nv_bfloat16* Ks = Qs + DAM_ROWS * QS;                                    // [64][QS]
-    __nv_bfloat16* Vs = Ks + DAM_KEYS * QS;                                    // [64][VS]
+    __nv_bfloat16* Ks0 = Qs + DAM_ROWS * QS;                                   // [2][64][QS]
+    __nv_bfloat16* Vs0 = Ks0 + 2 * DAM_KEYS * QS;                              // [2][64][VS]
     // ---- which tile
-    int b = blockIdx.x, req = -1, first = 0, n = 0, ctx_len = 0;
+    // (tiles later in a request see more keys: the grid is walked from its end so that they start first)
+    int b = gridDim.y - 1 - blockIdx.y, req = -1, first = 0, n = 0, ctx_len = 0;
     for (int r = 0; r < p.num_reqs; ++r) {
         const int t0 = p.cu_tokens[r], nr = p.cu_tokens[r + 1] - t0;
-        if (nr <= 0) continue;
+        if (nr <= 0 || (p.skip_single && nr == 1)) continue;
         const int tiles = (nr + DAM_ROWS - 1) / DAM_ROWS;
         if (b < tiles) { req = r; first = t0 + b * DAM_ROWS; n = min(DAM_ROWS, nr - b * DAM_ROWS); ctx_len = p.context_lens[r];
                          ctx_len = ctx_len - nr + b * DAM_ROWS; break; }      // position of the tile's first token
@@ -72,13 +80,13 @@ __global__ __launch_bounds__(128) void diff_attention_mma_kernel(const DamParams
     }
     if (req < 0) return;
     const int p0 = ctx_len;
-    const int head = blockIdx.y, kvh = head / (p.nh / p.nkv);
+    const int head = blockIdx.x, kvh = head / (p.nh / p.nkv);
     const int D = p.D, Dv = p.Dv, kd = 2 * D;
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31, g = lane >> 2, t = lane & 3;
     // ---- shared memory starts as zeros (the padding beyond D and Dv stays so), then the Q tile
     const bool vec = (D % 8 == 0) && (Dv % 8 == 0);
     {
-        constexpr int WORDS16 = (2 * DAM_ROWS * QS + DAM_KEYS * VS) / 8;
+        constexpr int WORDS16 = (3 * DAM_ROWS * QS + 2 * DAM_KEYS * VS) / 8;
         uint4* z = reinterpret_cast<uint4*>(dam_smem);
         for (int e = tid; e < WORDS16; e += 128) z[e] = make_uint4(0u, 0u, 0u, 0u);
     }
@@ -87,8 +95,7 @@ __global__ __launch_bounds__(128) void diff_attention_mma_kernel(const DamParams
         const int per = kd / 8;
         for (int e = tid; e < n * per; e += 128) {
             const int row = e / per, c = (e - row * per) * 8, m = c / D, d = c - m * D;
-            *reinterpret_cast<uint4*>(Qs + row * QS + m * DP + d) =
-                *reinterpret_cast<const uint4*>(p.q + ((size_t)(first + row) * p.nh + head) * kd + c);
+            cp_async16(Qs + row * QS + m * DP + d, p.q + ((size_t)(first + row) * p.nh + head) * kd + c);
         }
     } else {
         for (int e = tid; e < n * kd; e += 128) {
@@ -124,9 +131,12 @@ __global__ __launch_bounds__(128) void diff_attention_mma_kernel(const DamParams
     const int32_t* bt = p.block_table + (size_t)req * p.max_blocks;
     const float inv_cap = p.cap > 0.0f ? 1.0f / p.cap : 0.0f;
     bool bad = false;
-    for (int kbase = lo; kbase <= hi; kbase += DAM_KEYS) {
-        __syncthreads();                                   // the tile before is no longer read (and Qs is written)
-        // ---- K and V rows of up to 64 keys (rows beyond the last key keep what they held: they are masked)
+    // K and V rows of up to 64 keys from kbase on into stage `buf` (rows beyond the last key keep what they held:
+    // they are masked).  With 16-byte rows the copies are asynchronous and the next tile is on its way while
+    // this one is used.
+    auto load_tile = [&](int kbase, int buf) {
+        __nv_bfloat16* Ks = Ks0 + buf * DAM_KEYS * QS;
+        __nv_bfloat16* Vs = Vs0 + buf * DAM_KEYS * VS;
         const int nk = min(DAM_KEYS, hi - kbase + 1);
         const int perk = vec ? kd / 8 : kd, perv = vec ? Dv / 8 : Dv;
         for (int e = tid; e < nk * (perk + perv); e += 128) {
@@ -140,10 +150,10 @@ __global__ __launch_bounds__(128) void diff_attention_mma_kernel(const DamParams
             if (vec) {
                 if (u < perk) {
                     const int c = u * 8, m = c / D, d = c - m * D;
-                    *reinterpret_cast<uint4*>(Ks + key * QS + m * DP + d) = *reinterpret_cast<const uint4*>(pk + c);
+                    cp_async16(Ks + key * QS + m * DP + d, pk + c);
                 } else {
                     const int c = (u - perk) * 8;
-                    *reinterpret_cast<uint4*>(Vs + key * VS + c) = *reinterpret_cast<const uint4*>(pv + c);
+                    cp_async16(Vs + key * VS + c, pv + c);
                 }
             } else if (u < perk) {
                 const int m = u / D, d = u - m * D;
@@ -152,8 +162,22 @@ __global__ __launch_bounds__(128) void diff_attention_mma_kernel(const DamParams
                 Vs[key * VS + (u - perk)] = pv[u - perk];
             }
         }
+        cp_async_commit();
+    };
+    load_tile(lo, 0);
+    int it = 0;
+    for (int kbase = lo; kbase <= hi; kbase += DAM_KEYS, ++it) {
+        const int buf = it & 1;
+        const __nv_bfloat16* Ks = Ks0 + buf * DAM_KEYS * QS;
+        const __nv_bfloat16* Vs = Vs0 + buf * DAM_KEYS * VS;
+        if (kbase + DAM_KEYS <= hi) {
+            load_tile(kbase + DAM_KEYS, buf ^ 1);          // its stage was last read before the barrier that ended the tile before
+            cp_async_wait<1>();
+        } else {
+            cp_async_wait<0>();
+        }
         __syncthreads();
-        if (warp * 16 >= n) continue;                      // a warp without rows only helps to load
+        if (warp * 16 < n)                                 // a warp without rows only helps to load
 #pragma unroll
         for (int m = 0; m < 2; ++m) {
             float S[DAM_KEYS / 8][4];
@@ -175,28 +199,41 @@ __global__ __launch_bounds__(128) void diff_attention_mma_kernel(const DamParams
                     mma_bf16(S[nt], a, *reinterpret_cast<const uint32_t*>(kb), *reinterpret_cast<const uint32_t*>(kb + 8));
                 }
             }
-            // ---- scale, cap, mask, running maximum
+            // ---- scale, cap, mask, running maximum.  The cap c * tanh(x / c) = c - 2c / (exp(2x / c) + 1) with the
+            // scale and log2(e) folded into one factor; the mask only where a key of the tile can be hidden from a
+            // row of this warp; the exponentials in base 2 with the maximum folded into one multiply-add.
+            const float LOG2E = 1.4426950408889634f;
+            const float cap_in = 2.0f * p.scale * inv_cap * LOG2E, cap2 = -2.0f * p.cap;
+            const int row_lo = p0 + warp * 16, row_hi = min(p0 + warp * 16 + 15, hi);
+            int need_lo = lo;                               // the latest first-visible key among the warp's rows
+            if (p.chunk > 0) need_lo = max(need_lo, (row_hi / p.chunk) * p.chunk);
+            if (p.window > 0) need_lo = max(need_lo, row_hi - p.window + 1);
+            const bool masked = kbase + DAM_KEYS - 1 > row_lo || kbase < need_lo || warp * 16 + 15 >= n;
             float tmax[2] = {-INFINITY, -INFINITY};
 #pragma unroll
             for (int nt = 0; nt < DAM_KEYS / 8; ++nt)
 #pragma unroll
                 for (int j = 0; j < 4; ++j) {
-                    const int h = j >> 1, key = kbase + nt * 8 + 2 * t + (j & 1);
-                    float s = S[nt][j] * p.scale;
-                    if (p.cap > 0.0f) s = p.cap * tanh_exp(s * inv_cap);
-                    const bool vis = key <= pos[h] && key >= vis_lo[h];
-                    s = vis ? s : -INFINITY;
+                    const int h = j >> 1;
+                    float s;
+                    if (p.cap > 0.0f) s = fmaf(cap2, __fdividef(1.0f, exp2f(S[nt][j] * cap_in) + 1.0f), p.cap);
+                    else s = S[nt][j] * p.scale;
+                    if (masked) {
+                        const int key = kbase + nt * 8 + 2 * t + (j & 1);
+                        s = (key <= pos[h] && key >= vis_lo[h]) ? s : -INFINITY;
+                    }
                     S[nt][j] = s;
                     tmax[h] = fmaxf(tmax[h], s);
                 }
-            float corr[2], mnew[2];
+            float corr[2], mnew[2], mneg[2];
 #pragma unroll
             for (int h = 0; h < 2; ++h) {
                 tmax[h] = fmaxf(tmax[h], __shfl_xor_sync(0xffffffffu, tmax[h], 1));
                 tmax[h] = fmaxf(tmax[h], __shfl_xor_sync(0xffffffffu, tmax[h], 2));
                 mnew[h] = fmaxf(mx[m][h], tmax[h]);
-                corr[h] = mnew[h] == -INFINITY ? 1.0f : __expf(mx[m][h] - mnew[h]);      // exp(-inf) = 0 on the first keys
+                corr[h] = mnew[h] == -INFINITY ? 1.0f : exp2f((mx[m][h] - mnew[h]) * LOG2E);      // 0 on the first keys
                 mx[m][h] = mnew[h];
+                mneg[h] = mnew[h] == -INFINITY ? 0.0f : -mnew[h] * LOG2E;      // a row that sees nothing yet: exp2(-inf) = 0
             }
             float tsum[2] = {0.0f, 0.0f};
 #pragma unroll
@@ -204,7 +241,7 @@ __global__ __launch_bounds__(128) void diff_attention_mma_kernel(const DamParams
 #pragma unroll
                 for (int j = 0; j < 4; ++j) {
                     const int h = j >> 1;
-                    const float pr = mnew[h] == -INFINITY ? 0.0f : __expf(S[nt][j] - mnew[h]);
+                    const float pr = exp2f(fmaf(S[nt][j], LOG2E, mneg[h]));
                     S[nt][j] = pr;
                     tsum[h] += pr;
                 }
@@ -237,6 +274,7 @@ __global__ __launch_bounds__(128) void diff_attention_mma_kernel(const DamParams
                 }
             }
         }
+        __syncthreads();                                   // this stage may be written again
     }
     if (bad && lane == 0) atomicOr(p.err, AIRUN_DEV_BAD_PAGE);
     if (warp * 16 >= n) return;
@@ -272,15 +310,222 @@ __global__ __launch_bounds__(128) void diff_attention_mma_kernel(const DamParams
     }
 }
 
+// ---------------------------------------------------------------------------------------------------------
+// Single decoded tokens.  One CTA (8 warps) per (request that brings ONE token, KV head): all G query heads
+// of the group, both maps, share every key and value row that is read.  A group of GS lanes takes one key at a
+// time (a lane holds 8 consecutive elements of the key row and of the value row, read with one 16-byte load each);
+// the 256 / GS groups of the CTA walk the visible keys side by side, each with a running maximum, sum and value
+// accumulator per (head, map) in float32, and are merged at the end: first inside a warp by shuffles, then across
+// the warps through shared memory, in a fixed order.  Then o = a_1 - lambda * a_2 is normed per head and written.
+// D and Dv must be multiples of 8 (16-byte rows) with 2*D and Dv up to 8*GS; otherwise the tile kernel above
+// takes the token.
+template <int G, int GS>
+__global__ __launch_bounds__(256, (G <= 2 ? 2 : 1)) void diff_attention_decode_kernel(const DamParams p) {
+    pdl_trigger();
+    pdl_wait();
+    extern __shared__ __align__(16) unsigned char dam_smem[];
+    const int r = blockIdx.y, kvh = blockIdx.x;
+    const int t = p.cu_tokens[r];
+    if (p.cu_tokens[r + 1] - t != 1) return;
+    const int pos = p.context_lens[r] - 1;
+    const int D = p.D, Dv = p.Dv, kd = 2 * D;
+    const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31, li = tid % GS, worker = tid / GS;
+    constexpr int WORKERS = 256 / GS;
+    const bool k_on = li * 8 < kd, v_on = li * 8 < Dv;
+    const int my_map = li * 8 >= D ? 1 : 0;
+    float qf[G][8], acc[G][2][8], mx[G][2], sm[G][2];
+#pragma unroll
+    for (int g = 0; g < G; ++g) {
+        uint4 raw = make_uint4(0u, 0u, 0u, 0u);
+        if (k_on) raw = *reinterpret_cast<const uint4*>(p.q + ((size_t)t * p.nh + kvh * G + g) * kd + li * 8);
+        const __nv_bfloat162* h2 = reinterpret_cast<const __nv_bfloat162*>(&raw);
+#pragma unroll
+        for (int i = 0; i < 4; ++i) { const float2 f = __bfloat1622float2(h2[i]); qf[g][2 * i] = f.x; qf[g][2 * i + 1] = f.y; }
+#pragma unroll
+        for (int m = 0; m < 2; ++m) {
+            mx[g][m] = -INFINITY; sm[g][m] = 0.0f;
+#pragma unroll
+            for (int i = 0; i < 8; ++i) acc[g][m][i] = 0.0f;
+        }
+    }
+    int lo = p.chunk > 0 ? (pos / p.chunk) * p.chunk : 0;
+    if (p.window > 0) lo = max(lo, pos - p.window + 1);
+    const size_t page_elems = (size_t)p.nkv * p.page_size * (kd + Dv);
+    const int32_t* bt = p.block_table + (size_t)r * p.max_blocks;
+    const float inv_cap = p.cap > 0.0f ? 1.0f / p.cap : 0.0f;
+    bool bad = false;
+    // every group makes the same number of rounds (the shuffles below take whole warps); a group without a
+    // key in the last round reads nothing and leaves its sums alone
+    const int rounds = (pos - lo + WORKERS) / WORKERS;
+    constexpr int U = 4;                                   // rounds whose loads are issued before the first is used
+    for (int round0 = 0; round0 < rounds; round0 += U) {
+        uint4 kraw[U], vraw[U];
+        bool valid[U];
+#pragma unroll
+        for (int u = 0; u < U; ++u) {
+            const int j = lo + (round0 + u) * WORKERS + worker;
+            valid[u] = round0 + u < rounds && j <= pos;
+            const int blk = j / p.page_size;
+            const int page = valid[u] && blk < p.max_blocks ? bt[blk] : -1;
+            if (valid[u] && (page < 0 || page >= p.num_pages)) { bad = true; valid[u] = false; }
+            const __nv_bfloat16* pk = p.pool + (size_t)max(page, 0) * page_elems + ((size_t)kvh * p.page_size + (j - blk * p.page_size)) * kd;
+            const __nv_bfloat16* pv = p.pool + (size_t)max(page, 0) * page_elems + (size_t)p.nkv * p.page_size * kd +
+                                      ((size_t)kvh * p.page_size + (j - blk * p.page_size)) * Dv;
+            kraw[u] = make_uint4(0u, 0u, 0u, 0u);
+            vraw[u] = make_uint4(0u, 0u, 0u, 0u);
+            if (valid[u] && k_on) kraw[u] = *reinterpret_cast<const uint4*>(pk + li * 8);
+            if (valid[u] && v_on) vraw[u] = *reinterpret_cast<const uint4*>(pv + li * 8);
+        }
+#pragma unroll
+        for (int u = 0; u < U; ++u) {
+            if (round0 + u >= rounds) break;               // the same for every thread of the block
+            float kf[8], vf[8];
+            {
+                const __nv_bfloat162* k2 = reinterpret_cast<const __nv_bfloat162*>(&kraw[u]);
+                const __nv_bfloat162* v2 = reinterpret_cast<const __nv_bfloat162*>(&vraw[u]);
+#pragma unroll
+                for (int i = 0; i < 4; ++i) {
+                    const float2 a = __bfloat1622float2(k2[i]), b = __bfloat1622float2(v2[i]);
+                    kf[2 * i] = a.x; kf[2 * i + 1] = a.y; vf[2 * i] = b.x; vf[2 * i + 1] = b.y;
+                }
+            }
+#pragma unroll
+            for (int g = 0; g < G; ++g) {
+                float part = 0.0f;
+#pragma unroll
+                for (int i = 0; i < 8; ++i) part = fmaf(qf[g][i], kf[i], part);
+                float s[2] = {my_map == 0 ? part : 0.0f, my_map == 1 ? part : 0.0f};
+#pragma unroll
+                for (int o = GS / 2; o > 0; o >>= 1) {
+                    s[0] += __shfl_xor_sync(0xffffffffu, s[0], o);
+                    s[1] += __shfl_xor_sync(0xffffffffu, s[1], o);
+                }
+                if (valid[u])
+#pragma unroll
+                for (int m = 0; m < 2; ++m) {
+                    float sc = s[m] * p.scale;
+                    if (p.cap > 0.0f) sc = p.cap * tanh_exp(sc * inv_cap);
+                    const float mnew = fmaxf(mx[g][m], sc);
+                    const float corr = __expf(mx[g][m] - mnew), pr = __expf(sc - mnew);      // exp(-inf) = 0 on the first key
+                    sm[g][m] = sm[g][m] * corr + pr;
+#pragma unroll
+                    for (int i = 0; i < 8; ++i) acc[g][m][i] = fmaf(pr, vf[i], acc[g][m][i] * corr);
+                    mx[g][m] = mnew;
+                }
+            }
+        }
+    }
+    if (bad && li == 0) atomicOr(p.err, AIRUN_DEV_BAD_PAGE);
+    // ---- the groups of a warp into its first group
+#pragma unroll
+    for (int o = GS; o < 32; o <<= 1) {
+#pragma unroll
+        for (int g = 0; g < G; ++g)
+#pragma unroll
+            for (int m = 0; m < 2; ++m) {
+                const float m_o = __shfl_xor_sync(0xffffffffu, mx[g][m], o), s_o = __shfl_xor_sync(0xffffffffu, sm[g][m], o);
+                const float mnew = fmaxf(mx[g][m], m_o);
+                const float wa = mx[g][m] == -INFINITY ? 0.0f : __expf(mx[g][m] - mnew);
+                const float wb = m_o == -INFINITY ? 0.0f : __expf(m_o - mnew);
+                sm[g][m] = sm[g][m] * wa + s_o * wb;
+#pragma unroll
+                for (int i = 0; i < 8; ++i) {
+                    const float a_o = __shfl_xor_sync(0xffffffffu, acc[g][m][i], o);
+                    acc[g][m][i] = acc[g][m][i] * wa + a_o * wb;
+                }
+                mx[g][m] = mnew;
+            }
+    }
+    // ---- the warps through shared memory: [warp][g][m] -> maximum, sum, then 8*GS accumulator values
+    constexpr int ROW = 8 * GS + 2;
+    float* sh = reinterpret_cast<float*>(dam_smem);
+    if (lane < GS) {
+#pragma unroll
+        for (int g = 0; g < G; ++g)
+#pragma unroll
+            for (int m = 0; m < 2; ++m) {
+                float* row = sh + (size_t)((warp * G + g) * 2 + m) * ROW;
+                if (lane == 0) { row[0] = mx[g][m]; row[1] = sm[g][m]; }
+#pragma unroll
+                for (int i = 0; i < 8; ++i) row[2 + lane * 8 + i] = acc[g][m][i];
+            }
+    }
+    __syncthreads();
+    if (warp >= G) return;
+    const int g = warp, head = kvh * G + g;
+    float o[8];
+#pragma unroll
+    for (int i = 0; i < 8; ++i) o[i] = 0.0f;
+    const bool on = lane < GS && lane * 8 < Dv;
+#pragma unroll
+    for (int m = 0; m < 2; ++m) {
+        float gmax = -INFINITY, gsum = 0.0f, wgt[8];
+#pragma unroll
+        for (int w = 0; w < 8; ++w) gmax = fmaxf(gmax, sh[(size_t)((w * G + g) * 2 + m) * ROW]);
+#pragma unroll
+        for (int w = 0; w < 8; ++w) {
+            const float* row = sh + (size_t)((w * G + g) * 2 + m) * ROW;
+            wgt[w] = row[1] > 0.0f ? __expf(row[0] - gmax) : 0.0f;
+            gsum += row[1] * wgt[w];
+        }
+        const float inv = gsum > 0.0f ? 1.0f / gsum : 0.0f;
+        const float f = m == 0 ? inv : -p.lambda * inv;
+        if (on) {
+#pragma unroll
+            for (int i = 0; i < 8; ++i) {
+                float a = 0.0f;
+#pragma unroll
+                for (int w = 0; w < 8; ++w) a = fmaf(sh[(size_t)((w * G + g) * 2 + m) * ROW + 2 + lane * 8 + i], wgt[w], a);
+                o[i] = fmaf(a, f, o[i]);
+            }
+        }
+    }
+    float ss = 0.0f;
+#pragma unroll
+    for (int i = 0; i < 8; ++i) ss = fmaf(o[i], o[i], ss);
+    ss = warp_sum(ss);
+    const float nrm = p.out_scale / sqrtf(ss / (float)Dv + p.eps);
+    if (on) {
+        uint32_t w[4];
+#pragma unroll
+        for (int i = 0; i < 4; ++i) w[i] = pack_bf16(o[2 * i] * nrm, o[2 * i + 1] * nrm);
+        __nv_bfloat16* dst = p.out + (size_t)t * p.out_stride + (size_t)head * Dv + lane * 8;
+        if ((((size_t)dst) & 15) == 0) *reinterpret_cast<uint4*>(dst) = make_uint4(w[0], w[1], w[2], w[3]);
+        else {
+#pragma unroll
+            for (int i = 0; i < 4; ++i) *reinterpret_cast<uint32_t*>(dst + 2 * i) = w[i];
+        }
+    }
+}
+
+template <int G, int GS>
+static int dad_launch(const DamParams& p, cudaStream_t stream) {
+    const size_t smem = (size_t)8 * G * 2 * (8 * GS + 2) * sizeof(float);
+    static unsigned long long configured = 0;
+    if (smem > 48 * 1024 && first_on_device(configured)) {
+        cudaError_t e = cudaFuncSetAttribute(diff_attention_decode_kernel<G, GS>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+        if (e != cudaSuccess) return (int)e;
+    }
+    airun_launch(diff_attention_decode_kernel<G, GS>, dim3(p.nkv, p.num_reqs), dim3(256), smem, stream, p);
+    return airun_launch_status();
+}
+
+// 1 when the decode kernel takes these sizes (the caller then lets the tile kernel skip single tokens).
+AIRUN_EXPORT int airun_diff_attention_decode_supported(int nh, int nkv, int D, int Dv) {
+    const int G = nkv > 0 && nh % nkv == 0 ? nh / nkv : 0;
+    return (G == 1 || G == 2 || G == 4 || G == 8) && D % 8 == 0 && Dv % 8 == 0 && 2 * D <= 256 && Dv <= 256;
+}
+
 template <int DP, int DVP>
 static int dam_launch(const DamParams& p, int max_tiles, cudaStream_t stream) {
-    const size_t smem = (size_t)(2 * DAM_ROWS * (2 * DP + DAM_PAD) + DAM_KEYS * (DVP + DAM_PAD)) * sizeof(__nv_bfloat16);
+    const size_t smem = (size_t)(3 * DAM_ROWS * (2 * DP + DAM_PAD) + 2 * DAM_KEYS * (DVP + DAM_PAD)) * sizeof(__nv_bfloat16);
     static unsigned long long configured = 0;
     if (smem > 48 * 1024 && first_on_device(configured)) {
         cudaError_t e = cudaFuncSetAttribute(diff_attention_mma_kernel<DP, DVP>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
         if (e != cudaSuccess) return (int)e;
     }
-    airun_launch(diff_attention_mma_kernel<DP, DVP>, dim3(max_tiles, p.nh), dim3(128), smem, stream, p);
+    if (max_tiles > 65535) return AIRUN_ERR_ARG;
+    airun_launch(diff_attention_mma_kernel<DP, DVP>, dim3(p.nh, max_tiles), dim3(128), smem, stream, p);
     return airun_launch_status();
 }
 
@@ -289,7 +534,8 @@ AIRUN_EXPORT int airun_diff_attention_mma(const void* q, void* out, long long ou
                                           const int32_t* block_table, int max_blocks, const int32_t* cu_tokens,
                                           const int32_t* context_lens, int num_reqs, int max_tiles, int num_pages,
                                           int page_size, int nh, int nkv, int D, int Dv, float scale, float cap, int chunk,
-                                          int window, float lambda, float eps, float out_scale, int* err, cudaStream_t stream) {
+                                          int window, float lambda, float eps, float out_scale, int skip_single, int* err,
+                                          cudaStream_t stream) {
     if (num_reqs < 0 || max_tiles < 0 || nh <= 0 || nkv <= 0 || nh % nkv != 0 || D <= 0 || D > 128 || Dv <= 0 || Dv > 128 ||
         page_size <= 0 || num_pages <= 0 || max_blocks <= 0 || chunk < 0 || window < 0 || !err || nh > 65535 ||
         out_stride < (long long)nh * Dv || !cu_tokens || !context_lens)
@@ -300,12 +546,37 @@ AIRUN_EXPORT int airun_diff_attention_mma(const void* q, void* out, long long ou
     p.pool = (const __nv_bfloat16*)pool; p.block_table = block_table; p.max_blocks = max_blocks;
     p.cu_tokens = cu_tokens; p.context_lens = context_lens; p.num_reqs = num_reqs; p.num_pages = num_pages;
     p.page_size = page_size; p.nh = nh; p.nkv = nkv; p.D = D; p.Dv = Dv; p.scale = scale; p.cap = cap;
-    p.lambda = lambda; p.eps = eps; p.out_scale = out_scale; p.chunk = chunk; p.window = window; p.err = err;
+    p.lambda = lambda; p.eps = eps; p.out_scale = out_scale; p.chunk = chunk; p.window = window; p.skip_single = skip_single; p.err = err;
     const int dp = D <= 32 ? 32 : D <= 64 ? 64 : 128, dvp = Dv <= 32 ? 32 : Dv <= 64 ? 64 : 128;
 #define DAM_CASE(A, B) if (dp == A && dvp == B) return dam_launch<A, B>(p, max_tiles, stream)
     DAM_CASE(32, 32); DAM_CASE(32, 64); DAM_CASE(32, 128);
     DAM_CASE(64, 32); DAM_CASE(64, 64); DAM_CASE(64, 128);
     DAM_CASE(128, 32); DAM_CASE(128, 64); DAM_CASE(128, 128);
 #undef DAM_CASE
+    return AIRUN_ERR_UNSUPPORTED;
+}
+
+// The single tokens of the batch (requests whose cu_tokens span is 1); every other request is skipped.
+AIRUN_EXPORT int airun_diff_attention_decode(const void* q, void* out, long long out_stride, const void* pool,
+                                             const int32_t* block_table, int max_blocks, const int32_t* cu_tokens,
+                                             const int32_t* context_lens, int num_reqs, int num_pages, int page_size,
+                                             int nh, int nkv, int D, int Dv, float scale, float cap, int chunk, int window,
+                                             float lambda, float eps, float out_scale, int* err, cudaStream_t stream) {
+    if (num_reqs < 0 || nh <= 0 || nkv <= 0 || page_size <= 0 || num_pages <= 0 || max_blocks <= 0 || chunk < 0 || window < 0 ||
+        !err || out_stride < (long long)nh * Dv || !cu_tokens || !context_lens || num_reqs > 65535 ||
+        !airun_diff_attention_decode_supported(nh, nkv, D, Dv) || (((uintptr_t)q | (uintptr_t)pool) & 15))
+        return AIRUN_ERR_ARG;
+    if (num_reqs == 0) return AIRUN_OK;
+    DamParams p;
+    p.q = (const __nv_bfloat16*)q; p.out = (__nv_bfloat16*)out; p.out_stride = out_stride;
+    p.pool = (const __nv_bfloat16*)pool; p.block_table = block_table; p.max_blocks = max_blocks;
+    p.cu_tokens = cu_tokens; p.context_lens = context_lens; p.num_reqs = num_reqs; p.num_pages = num_pages;
+    p.page_size = page_size; p.nh = nh; p.nkv = nkv; p.D = D; p.Dv = Dv; p.scale = scale; p.cap = cap;
+    p.lambda = lambda; p.eps = eps; p.out_scale = out_scale; p.chunk = chunk; p.window = window; p.skip_single = 0; p.err = err;
+    const int G = nh / nkv, width = 2 * D > Dv ? 2 * D : Dv, gs = width <= 64 ? 8 : width <= 128 ? 16 : 32;
+#define DAD_CASE(A, B) if (G == A && gs == B) return dad_launch<A, B>(p, stream)
+    DAD_CASE(1, 8); DAD_CASE(1, 16); DAD_CASE(1, 32); DAD_CASE(2, 8); DAD_CASE(2, 16); DAD_CASE(2, 32);
+    DAD_CASE(4, 8); DAD_CASE(4, 16); DAD_CASE(4, 32); DAD_CASE(8, 8); DAD_CASE(8, 16); DAD_CASE(8, 32);
+#undef DAD_CASE
     return AIRUN_ERR_UNSUPPORTED;
 }

@@ -53,11 +53,17 @@ AIRUN_EXPORT int airun_gla_log_decay(const float* low, long long low_stride, con
 }
 
 // The recurrence.  One block per (request, head, 32 value columns), 256 threads: a warp owns four
-// columns, and the eight lanes of a column own the key channels d = i * 8 + part (i < NS), so a thread
+// columns, and the eight lanes of a column own the key channels d = 32 * (i / 4) + 4 * part + i % 4
+// (i < NS: runs of four, so that q, k and the decay come from shared memory as float4), so a thread
 // keeps NS elements of the state in registers for the whole step.  The tokens of the request are
-// staged through shared memory a few at a time (q, k, exp(log a) per key channel, v per column), each
-// thread updates its strip and the eight partial sums of a column are added by shuffles.
+// staged through shared memory a few at a time (q, k, log a per key channel, v per column) by
+// asynchronous copies into one of two stages, so that the next tokens are on their way while these are
+// used; exp(log a) is taken once per staged element.  Each thread updates its strip and the eight
+// partial sums of a column are added by shuffles.
 #define GLA_COLS 32
+__device__ __forceinline__ void gla_cp4(float* smem, const float* gmem) {
+    asm volatile("cp.async.ca.shared.global [%0], [%1], 4;" ::"r"((uint32_t)__cvta_generic_to_shared(smem)), "l"(gmem) : "memory");
+}
 template <int NS>
 __global__ __launch_bounds__(256) void gla_recurrent_kernel(
     const float* __restrict__ q, const float* __restrict__ k, const float* __restrict__ v, long long row_stride,
@@ -67,8 +73,8 @@ __global__ __launch_bounds__(256) void gla_recurrent_kernel(
     pdl_trigger();
     pdl_wait();
     constexpr int DP = NS * 8;
-    constexpr int GLA_TT = NS >= 32 ? 8 : 16;        // tokens staged at a time (static shared memory stays under 48 KB)
-    __shared__ float s_q[GLA_TT][DP], s_k[GLA_TT][DP], s_a[GLA_TT][DP], s_v[GLA_TT][GLA_COLS];
+    constexpr int GLA_TT = NS >= 32 ? 4 : NS >= 16 ? 8 : 16;     // tokens of a stage (static shared memory stays under 48 KB)
+    __shared__ __align__(16) float s_q[2][GLA_TT][DP], s_k[2][GLA_TT][DP], s_a[2][GLA_TT][DP], s_v[2][GLA_TT][GLA_COLS];
     const int r = blockIdx.x, head = blockIdx.y, col0 = blockIdx.z * GLA_COLS;
     const int t0 = cu_tokens[r], n = cu_tokens[r + 1] - t0;
     if (n <= 0) return;
@@ -80,51 +86,77 @@ __global__ __launch_bounds__(256) void gla_recurrent_kernel(
     const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
     const int part = lane & 7, cw = warp * 4 + (lane >> 3), col = col0 + cw;
     const bool col_ok = col < Dv;
+    // the padding beyond D and Dv is zero in both stages and is never copied into
+    for (int e = threadIdx.x; e < 2 * GLA_TT * DP; e += 256) {
+        (&s_q[0][0][0])[e] = 0.0f; (&s_k[0][0][0])[e] = 0.0f; (&s_a[0][0][0])[e] = 0.0f;
+    }
+    for (int e = threadIdx.x; e < 2 * GLA_TT * GLA_COLS; e += 256) (&s_v[0][0][0])[e] = 0.0f;
+    __syncthreads();
+    auto stage = [&](int base, int buf) {
+        const int nt = min(GLA_TT, n - base);
+        for (int e = threadIdx.x; e < nt * D; e += 256) {
+            const int tt = e / D, d = e - tt * D;
+            const size_t row = (size_t)(t0 + base + tt);
+            gla_cp4(&s_q[buf][tt][d], q + row * row_stride + (size_t)head * D + d);
+            gla_cp4(&s_k[buf][tt][d], k + row * row_stride + (size_t)head * D + d);
+            gla_cp4(&s_a[buf][tt][d], log_decay + row * ((size_t)heads * D) + (size_t)head * D + d);
+        }
+        const int nc = min(GLA_COLS, Dv - col0);
+        for (int e = threadIdx.x; e < nt * nc; e += 256) {
+            const int tt = e / nc, c = e - tt * nc;
+            gla_cp4(&s_v[buf][tt][c], v + (size_t)(t0 + base + tt) * row_stride + (size_t)head * Dv + col0 + c);
+        }
+        asm volatile("cp.async.commit_group;" ::: "memory");
+    };
+    stage(0, 0);
     float* srow = state + (size_t)slot * slot_stride + ((size_t)head * Dv + (col_ok ? col : 0)) * D;
     float S[NS];
 #pragma unroll
     for (int i = 0; i < NS; ++i) {
-        const int d = i * 8 + part;
+        const int d = 32 * (i / 4) + 4 * part + (i % 4);
         S[i] = (col_ok && d < D) ? srow[d] : 0.0f;
     }
-    for (int base = 0; base < n; base += GLA_TT) {
-        const int nt = min(GLA_TT, n - base);
-        __syncthreads();
-        for (int e = threadIdx.x; e < nt * DP; e += 256) {
-            const int tt = e / DP, d = e - tt * DP;
-            const size_t row = (size_t)(t0 + base + tt);
-            float qv = 0.0f, kv = 0.0f, av = 0.0f;
-            if (d < D) {
-                qv = q[row * row_stride + (size_t)head * D + d];
-                kv = k[row * row_stride + (size_t)head * D + d];
-                av = expf(log_decay[row * ((size_t)heads * D) + (size_t)head * D + d]);
-            }
-            s_q[tt][d] = qv; s_k[tt][d] = kv; s_a[tt][d] = av;
-        }
-        for (int e = threadIdx.x; e < nt * GLA_COLS; e += 256) {
-            const int tt = e / GLA_COLS, c = e - tt * GLA_COLS;
-            s_v[tt][c] = (col0 + c < Dv) ? v[(size_t)(t0 + base + tt) * row_stride + (size_t)head * Dv + col0 + c] : 0.0f;
+    int it = 0;
+    for (int base = 0; base < n; base += GLA_TT, ++it) {
+        const int buf = it & 1, nt = min(GLA_TT, n - base);
+        if (base + GLA_TT < n) {
+            stage(base + GLA_TT, buf ^ 1);          // that stage was last read before the barrier that ended the round before
+            asm volatile("cp.async.wait_group 1;" ::: "memory");
+        } else {
+            asm volatile("cp.async.wait_group 0;" ::: "memory");
         }
         __syncthreads();
+        for (int e = threadIdx.x; e < nt * D; e += 256) {
+            const int tt = e / D, d = e - tt * D;
+            s_a[buf][tt][d] = expf(s_a[buf][tt][d]);
+        }
+        __syncthreads();
+#pragma unroll 4
         for (int tt = 0; tt < nt; ++tt) {
-            const float vj = s_v[tt][cw];
+            const float vj = s_v[buf][tt][cw];
             float acc = 0.0f;
 #pragma unroll
-            for (int i = 0; i < NS; ++i) {
-                const int d = i * 8 + part;
-                S[i] = fmaf(s_a[tt][d], S[i], s_k[tt][d] * vj);
-                acc = fmaf(S[i], s_q[tt][d], acc);
+            for (int i4 = 0; i4 < NS / 4; ++i4) {
+                const int d = 32 * i4 + 4 * part;
+                const float4 a4 = *reinterpret_cast<const float4*>(&s_a[buf][tt][d]);
+                const float4 k4 = *reinterpret_cast<const float4*>(&s_k[buf][tt][d]);
+                const float4 q4 = *reinterpret_cast<const float4*>(&s_q[buf][tt][d]);
+                S[4 * i4 + 0] = fmaf(a4.x, S[4 * i4 + 0], k4.x * vj); acc = fmaf(S[4 * i4 + 0], q4.x, acc);
+                S[4 * i4 + 1] = fmaf(a4.y, S[4 * i4 + 1], k4.y * vj); acc = fmaf(S[4 * i4 + 1], q4.y, acc);
+                S[4 * i4 + 2] = fmaf(a4.z, S[4 * i4 + 2], k4.z * vj); acc = fmaf(S[4 * i4 + 2], q4.z, acc);
+                S[4 * i4 + 3] = fmaf(a4.w, S[4 * i4 + 3], k4.w * vj); acc = fmaf(S[4 * i4 + 3], q4.w, acc);
             }
             acc += __shfl_xor_sync(0xffffffffu, acc, 1);
             acc += __shfl_xor_sync(0xffffffffu, acc, 2);
             acc += __shfl_xor_sync(0xffffffffu, acc, 4);
             if (part == 0 && col_ok) out[(size_t)(t0 + base + tt) * ((size_t)heads * Dv) + (size_t)head * Dv + col] = acc * q_scale;
         }
+        __syncthreads();
     }
     if (col_ok) {
 #pragma unroll
         for (int i = 0; i < NS; ++i) {
-            const int d = i * 8 + part;
+            const int d = 32 * (i / 4) + 4 * part + (i % 4);
             if (d < D) srow[d] = S[i];
         }
     }

@@ -571,14 +571,24 @@ def diff_attention_bf16(ctx, q, out, cache, part) -> bool:
     _need(pool.is_contiguous() and pool[0].numel() == nkv * cache.page_size * (2 * D + Dv), "the cache pages do not fit the head sizes")
     _need(ctx.cu_tokens.numel() >= ctx.num_reqs + 1 and ctx.context_lens.numel() >= ctx.num_reqs,
           "the batch's layout arrays are shorter than its number of requests")
-    # every request's tokens are cut into tiles of 64; the kernel walks cu_tokens to find its tile, so the
+    common = [_p(q), _p(out), out.stride(0) if T > 1 else max(out.shape[1], out.stride(0)), _p(pool), _p(bt), bt.stride(0),
+              _p(ctx.cu_tokens), _p(ctx.context_lens), int(ctx.num_reqs)]
+    consts = [pool.shape[0], int(cache.page_size), nh, nkv, D, Dv, float(part.scale), float(part.cap), int(part.chunk),
+              int(part.window), float(part.lam), float(part.eps), 1.0 - float(part.lambda_init)]
+    sig = [c_void_p, c_void_p, c_longlong, c_void_p, c_void_p, c_int, c_void_p, c_void_p, c_int]
+    csig = [c_int, c_int, c_int, c_int, c_int, c_int, c_float, c_float, c_int, c_int, c_float, c_float, c_float]
+    # requests that bring ONE token go to the decode kernel (all query heads of a KV head share each key read) when
+    # it takes the sizes; it finds them on the device, and the tile kernel then skips them
+    single = "diff_decode" not in DISABLED and nh // nkv in (1, 2, 4, 8) and D % 8 == 0 and Dv % 8 == 0 \
+        and q.data_ptr() % 16 == 0 and pool.data_ptr() % 16 == 0
+    if single:
+        f = _fn("diff_attention_mma", "airun_diff_attention_decode", sig + csig + [c_void_p, c_void_p])
+        _check(f(*common, *consts, _p(ctx.err), _stream()), "diff_attention_decode")
+        if getattr(ctx, "decode_only", False):
+            return True
+    # every other request's tokens are cut into tiles of 64; the kernel walks cu_tokens to find its tile, so the
     # launch only needs an upper bound of their number
     max_tiles = (T + DIFF_TILE_ROWS - 1) // DIFF_TILE_ROWS + int(ctx.num_reqs)
-    f = _fn("diff_attention_mma", "airun_diff_attention_mma",
-            [c_void_p, c_void_p, c_longlong, c_void_p, c_void_p, c_int, c_void_p, c_void_p, c_int, c_int, c_int, c_int,
-             c_int, c_int, c_int, c_int, c_float, c_float, c_int, c_int, c_float, c_float, c_float, c_void_p, c_void_p])
-    _check(f(_p(q), _p(out), out.stride(0) if T > 1 else max(out.shape[1], out.stride(0)), _p(pool), _p(bt), bt.stride(0),
-             _p(ctx.cu_tokens), _p(ctx.context_lens), int(ctx.num_reqs), max_tiles, pool.shape[0], int(cache.page_size),
-             nh, nkv, D, Dv, float(part.scale), float(part.cap), int(part.chunk), int(part.window), float(part.lam),
-             float(part.eps), 1.0 - float(part.lambda_init), _p(ctx.err), _stream()), "diff_attention_mma")
+    f = _fn("diff_attention_mma", "airun_diff_attention_mma", sig + [c_int] + csig + [c_int, c_void_p, c_void_p])
+    _check(f(*common, max_tiles, *consts, 1 if single else 0, _p(ctx.err), _stream()), "diff_attention_mma")
     return True

@@ -503,6 +503,162 @@ def workload_ablate(a) -> int:
     return 0
 
 
+# ---------------------------------------------------------------------------------------------------------
+# The Vedizen design beside the dense Qwen3 decoder at equal size (--workload vedizen)
+VEDIZEN_SIZES = {
+    # width, feed-forward, heads, KV heads: the layer sizes of the Qwen3-1.7B and Qwen3-8B shapes
+    "2048": dict(width=2048, ff=6144, heads=16, kv_heads=8),
+    "4096": dict(width=4096, ff=12288, heads=32, kv_heads=8),
+}
+VEDIZEN_VOCAB, VEDIZEN_RUNS = 32768, 6
+
+
+def vedizen_pair(size: dict):
+    """(Vedizen configuration, Qwen3 configuration) with the same width, feed-forward size, head counts, vocabulary
+    and six layer runs a token: four Vedizen layers (gated linear attention, two differential attention layers with
+    chunks of 2,048 positions, gated linear attention) of which the first two run twice, against six Qwen3 layers.
+    A differential attention layer has exactly the weights of a Qwen3 layer (two query/key maps of 64 where Qwen3 has
+    one of 128); a gated linear attention layer has a third more in its mixer."""
+    from airun_b200 import Qwen3Config, VedizenConfig
+    W, F, H, G = size["width"], size["ff"], size["heads"], size["kv_heads"]
+    mlp = dict(kind="dense", ff=F, limit=7.0)
+    gla = dict(type="gla", mixer=dict(heads=H, dim=64, vdim=128, tau=16.0), mlp=mlp)
+    att = dict(type="attention", mixer=dict(heads=H, kv_heads=G, dim=64, vdim=128, scale=0.125, softcap=50.0, diff=0.5,
+                                            mask=dict(size=2048)), mlp=mlp)
+    ved = VedizenConfig.from_dict(dict(architecture="Vedizen", vocab=VEDIZEN_VOCAB, width=W, embedding=dict(scale=1.0),
+                                       norm=dict(eps=1e-5), layers=[gla, att, att, gla], loop=dict(start=0, stop=2, times=2)))
+    qw = Qwen3Config.from_dict(dict(QWEN3_8B, vocab_size=VEDIZEN_VOCAB, hidden_size=W, num_hidden_layers=VEDIZEN_RUNS,
+                                    num_attention_heads=H, num_key_value_heads=G, head_dim=128, intermediate_size=F))
+    return ved, qw
+
+
+def fill_states(eng, seed=1):
+    import torch
+    g = torch.Generator(device=eng.device)
+    g.manual_seed(seed)
+    for st in eng.storage.state:
+        st.copy_(torch.randn(st.shape, generator=g, device=eng.device, dtype=torch.float32).mul_(0.1))
+
+
+def time_decode_onward(eng, batch, context, steps, warmup, tag):
+    """Device time of a decode step of ``batch`` requests whose contexts begin at ``context`` and grow as they
+    decode (requests with a recurrent state cannot be cut back between repeats): median of three repeats."""
+    import torch
+    from airun_b200 import StepEntry
+    from airun_b200.kernels import ops
+    rids = [f"{tag}{i}" for i in range(batch)]
+    fill_contexts(eng, rids, context)
+    fill_states(eng)
+    toks = torch.randint(0, eng.config.vocab_size, (batch,), generator=torch.Generator().manual_seed(1)).tolist()
+    picked = torch.zeros(batch, dtype=torch.int32, device=eng.device)
+    entries = [StepEntry(r, [toks[j]], (0,)) for j, r in enumerate(rids)]
+
+    def one():
+        ops.sample(eng.runner.step(entries), picked)
+
+    for _ in range(warmup):
+        one()
+    times = []
+    for _ in range(3):
+        torch.cuda.synchronize()
+        ev0, ev1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        ev0.record()
+        for _ in range(steps):
+            one()
+        ev1.record()
+        torch.cuda.synchronize()
+        times.append(ev0.elapsed_time(ev1) / steps)
+    eng.runner.raise_on_device_error()
+    for r in rids:
+        eng.manager.free_request(r)
+    return statistics.median(times)
+
+
+def workload_vedizen(a) -> int:
+    """Prefill (one 2,048-token prompt) and decode (batch 8 and 64 at a context of 1,024) of the Vedizen design and of
+    the Qwen3 decoder at equal size, through the step function and its CUDA graphs, and what each kind of kernel of the
+    two adds to the prefill step and to the batch-64 decode step (the step timed again with that kind left out), with
+    the fraction of the measured peak that its bytes or FLOPs over that time come to.  One JSON line per size."""
+    import torch
+    from airun_b200 import Engine, EngineOptions
+    from airun_b200.kernels import fast, ops
+    pk = peaks()
+    T, ctx_len, steps = 2048, 1024, max(8, min(a.steps, 32))
+    fp32_peak = 148 * 128 * 2 * 1.965e9          # FMA lanes x 2 x the highest SM clock: nominal, no measured figure
+    for name in (a.sizes.split(",") if a.sizes else list(VEDIZEN_SIZES)):
+        size = VEDIZEN_SIZES[name]
+        W, F, H, G = size["width"], size["ff"], size["heads"], size["kv_heads"]
+        line = {"workload": "vedizen", "size": size, "layer_runs": VEDIZEN_RUNS, "vocab": VEDIZEN_VOCAB, "dtype": "bf16",
+                "data": "synthetic, random weights", "prompt": T, "decode_context": ctx_len, "peaks": pk["source"], "models": {}}
+        for model, cfg in zip(("vedizen", "qwen3"), vedizen_pair(size)):
+            eng = Engine.from_config(cfg, seed=0, options=EngineOptions(
+                dtype="bfloat16", page_size=16, cache_tokens=64 * (ctx_len + 4 * steps + 64) + 4096, max_batch_tokens=T,
+                max_requests=64, max_context=max(T, ctx_len + 4 * steps + 64)))
+            kinds = {}                       # kind -> (module, function name, bytes or FLOPs at prefill, at batch 64, bound)
+            if model == "vedizen":
+                n_att, n_gla = 3, 3          # runs of each mixer among the six
+                kinds["norm (dynamic tanh)"] = (ops, "dyt_norm", lambda t: 7 * t * W * 14.0, "hbm")
+                kinds["q/k/v bias + cache write"] = (ops, "qkv_bias_store", lambda t: n_att * t * ((H + G) * 128 + G * 128) * 6.0, "hbm")
+                kinds["differential attention"] = (fast, "diff_attention_bf16", None, "mixed")
+                kinds["linear attention: decay"] = (ops, "gla_log_decay", lambda t: n_gla * t * H * 64 * 4.0, "hbm")
+                kinds["linear attention: recurrence"] = (ops, "gla_recurrent", None, "mixed")
+                kinds["linear attention: norm and gate"] = (ops, "gla_out_gate", lambda t: n_gla * t * H * 128 * 10.0, "hbm")
+                kinds["gate/up product + gated unit"] = (fast, "linear_glu_clamped_bf16", lambda t: 6 * 2.0 * t * W * 2 * F, "tensor")
+                att_flops = n_att * H * 2 * (2 * 64 + 2 * 128) * T * (T + 1) / 2
+                att_bytes = lambda b, c: n_att * b * c * G * (128 + 128) * 2.0
+                rec_flops = n_gla * T * H * 64 * 128 * 5.0
+                rec_bytes = lambda b: n_gla * b * H * 64 * 128 * 4.0 * 2
+            else:
+                kinds["norm (rms)"] = (ops, "rmsnorm", lambda t: 13 * t * W * 14.0, "hbm")
+                kinds["q/k norm + rotary + cache write"] = (ops, "qkv_post", lambda t: 6 * t * (H + 2 * G) * 128 * 6.0, "hbm")
+                kinds["attention"] = (fast, "attention_bf16", None, "mixed")
+                kinds["gate/up product + gated unit"] = (fast, "linear_swiglu_bf16", lambda t: 6 * 2.0 * t * W * 2 * F, "tensor")
+                att_flops = 6 * H * 4 * 128 * T * (T + 1) / 2
+                att_bytes = lambda b, c: 6 * b * c * G * 256 * 2.0
+            res = {}
+            base = {}
+
+            def measure():
+                eng.runner.graphs.clear()
+                eng.runner._warm_buckets.clear()
+                return dict(prefill=time_prefill(eng, T), b64=time_decode_onward(eng, 64, ctx_len, steps, a.warmup, "v"))
+
+            base = measure()
+            b8 = time_decode_onward(eng, 8, ctx_len, steps, a.warmup, "w")
+            res["prefill"] = {"ms": round(base["prefill"], 3), "tokens_per_s": round(T / base["prefill"] * 1e3, 1)}
+            res["decode_b8"] = {"ms_per_step": round(b8, 4), "tokens_per_s": round(8 / b8 * 1e3, 1)}
+            res["decode_b64"] = {"ms_per_step": round(base["b64"], 4), "tokens_per_s": round(64 / base["b64"] * 1e3, 1)}
+            res["kernels"] = {}
+            for kind, (mod, fn, work, bound) in kinds.items():
+                real = getattr(mod, fn)
+                setattr(mod, fn, (lambda *x, **k: True) if mod is fast else (lambda *x, **k: None))
+                try:
+                    left = measure()
+                finally:
+                    setattr(mod, fn, real)
+                pre_us, dec_us = (base["prefill"] - left["prefill"]) * 1e3, (base["b64"] - left["b64"]) * 1e3
+                row = {"prefill_us": round(pre_us, 1), "decode_b64_us": round(dec_us, 1)}
+                if kind in ("differential attention", "attention"):
+                    row["prefill_frac_of_bf16_peak"] = round(att_flops / max(pre_us, 1e-3) / 1e6 / (pk["bf16_tflops"] * 1e12) * 1e12, 4)
+                    row["decode_b64_frac_of_hbm"] = round(att_bytes(64, ctx_len) / max(dec_us, 1e-3) / 1e3 / pk["hbm_gbs"], 4)
+                elif kind == "linear attention: recurrence":
+                    row["prefill_frac_of_nominal_fp32"] = round(rec_flops / max(pre_us, 1e-3) * 1e6 / fp32_peak, 4)
+                    row["decode_b64_frac_of_hbm"] = round(rec_bytes(64) / max(dec_us, 1e-3) / 1e3 / pk["hbm_gbs"], 4)
+                elif bound == "hbm":
+                    row["prefill_frac_of_hbm"] = round(work(T) / max(pre_us, 1e-3) / 1e3 / pk["hbm_gbs"], 4)
+                    row["decode_b64_frac_of_hbm"] = round(work(64) / max(dec_us, 1e-3) / 1e3 / pk["hbm_gbs"], 4)
+                else:
+                    row["prefill_frac_of_bf16_peak"] = round(work(T) / max(pre_us, 1e-3) * 1e6 / (pk["bf16_tflops"] * 1e12), 4)
+                    row["decode_b64_frac_of_hbm"] = round(6 * 2.0 * W * 2 * F / max(dec_us, 1e-3) / 1e3 / pk["hbm_gbs"], 4)
+                res["kernels"][kind] = row
+            line["models"][model] = res
+            del eng
+            torch.cuda.empty_cache()
+        print(json.dumps(line), flush=True)
+    return 0
+
+
+
 def reference_arm(a) -> int:
     """The same metric on the reference's own CUDA kernels (compiled unmodified for sm_100), called
     through their C entry points in the order the reference's runtime calls them
@@ -682,10 +838,12 @@ def main() -> int:
     ap.add_argument("--skip-points", action="store_true")
     ap.add_argument("--decode-only", action="store_true", help="time the decode step only (for profiling runs)")
     ap.add_argument("--prefill-only", action="store_true", help="time the 2,048-token prompt only (for profiling runs)")
-    ap.add_argument("--workload", default="decode", choices=("decode", "serve", "long", "ablate"),
+    ap.add_argument("--workload", default="decode", choices=("decode", "serve", "long", "ablate", "vedizen"),
                     help="decode: the headline line; serve: 128 requests continuously batched (Qwen3-1.7B shape); "
                          "long: a 32,768-token prompt, then decoding alone and as 16 forks (Qwen3-32B shape); "
-                         "ablate: the decode step timed with one kind of kernel left out at a time")
+                         "ablate: the decode step timed with one kind of kernel left out at a time; "
+                         "vedizen: prefill and decode of the Vedizen design beside the Qwen3 decoder at equal size")
+    ap.add_argument("--sizes", default="", help="vedizen: widths to run, comma separated (default: 2048,4096)")
     ap.add_argument("--requests", type=int, default=128, help="serve: requests")
     ap.add_argument("--new-tokens", type=int, default=None, help="serve / long: tokens decoded per request")
     ap.add_argument("--budget", type=int, default=512, help="serve: tokens per step")
@@ -706,6 +864,8 @@ def main() -> int:
         return workload_long(a)
     if a.workload == "ablate":
         return workload_ablate(a)
+    if a.workload == "vedizen":
+        return workload_vedizen(a)
 
     import torch
     from airun_b200 import Engine, EngineOptions, Qwen3Config
