@@ -4,20 +4,20 @@
 //     S[d][j] <- a_t[d] * S[d][j] + k_t[d] * v_t[j]          o_t[j] = sum_d S[d][j] * q_t[d] * q_scale
 // (the output uses the state AFTER the token's own update).  The decay a_t[d] lies in (0, 1):
 //     a_t = sigmoid(z_t)^(1/tau),  z_t = W2 (low_t) + bias,   low_t = the low-rank projection of the input,
-// kept as its logarithm  log a = logsigmoid(z) / tau  (log_decay_kernel), which is what a chunked form sums.
+// computed as  a = exp(logsigmoid(z) / tau)  (decay_kernel).
 // Then, per head, o_t is divided by its root mean square over Dv (eps inside the root), multiplied by a
 // weight vector shared by the heads and by silu of a gate projection (out_gate_kernel).
 //
 // State, decays, the recurrence and the norm are float32 whatever the storage of the activations.  The
-// state of a request lives in its slot of the state tensor between steps, stored per head as [Dv][D]
-// (the key channels of one value column side by side), and is zero when the request starts.  The result
+// state of a request lives in its slot of the state tensor between steps, stored per head as [D][Dv]
+// (a row per key channel, the value columns side by side), and is zero when the request starts.  The result
 // at a token depends only on the request's tokens up to it, not on how they were cut into steps or on
 // what else is in the batch: the recurrence runs token by token in every case.
 #include "common.cuh"
 
-// log a[t][c] = logsigmoid(bias[c] + sum_j low[t][j] * w2[c][j]) / tau for c < n (= heads * D).
+// a[t][c] = exp(logsigmoid(bias[c] + sum_j low[t][j] * w2[c][j]) / tau) for c < n (= heads * D).
 template <typename TW>
-__global__ void log_decay_kernel(const float* __restrict__ low, long long low_stride, const TW* __restrict__ w2,
+__global__ void decay_kernel(const float* __restrict__ low, long long low_stride, const TW* __restrict__ w2,
                                  const float* __restrict__ bias, float* __restrict__ out, int n, int rank,
                                  float inv_tau, const int32_t* __restrict__ req_of_token) {
     pdl_trigger();
@@ -33,48 +33,54 @@ __global__ void log_decay_kernel(const float* __restrict__ low, long long low_st
         for (int j = 0; j < rank; ++j) z = fmaf(s_low[j], to_f32<TW>(wr[j]), z);
         // logsigmoid(z) = min(z, 0) - log(1 + exp(-|z|))
         const float ls = fminf(z, 0.0f) - log1pf(expf(-fabsf(z)));
-        out[(size_t)t * n + c] = ls * inv_tau;
+        out[(size_t)t * n + c] = expf(ls * inv_tau);
     }
 }
 
-AIRUN_EXPORT int airun_gla_log_decay(const float* low, long long low_stride, const void* w2, int w_dtype, const float* bias,
+AIRUN_EXPORT int airun_gla_decay(const float* low, long long low_stride, const void* w2, int w_dtype, const float* bias,
                                      float* out, int T, int n, int rank, float tau, const int32_t* req_of_token,
                                      cudaStream_t stream) {
     if (T < 0 || n <= 0 || rank <= 0 || rank > 8192 || !(tau > 0.0f) || !req_of_token) return AIRUN_ERR_ARG;
     if (T == 0) return AIRUN_OK;
     const size_t smem = (size_t)rank * sizeof(float);
     if (w_dtype == AIRUN_DT_F32)
-        airun_launch(log_decay_kernel<float>, dim3(T), dim3(128), smem, stream, low, low_stride, (const float*)w2, bias, out, n, rank, 1.0f / tau, req_of_token);
+        airun_launch(decay_kernel<float>, dim3(T), dim3(128), smem, stream, low, low_stride, (const float*)w2, bias, out, n, rank, 1.0f / tau, req_of_token);
     else if (w_dtype == AIRUN_DT_BF16)
-        airun_launch(log_decay_kernel<__nv_bfloat16>, dim3(T), dim3(128), smem, stream, low, low_stride, (const __nv_bfloat16*)w2, bias, out, n, rank, 1.0f / tau, req_of_token);
+        airun_launch(decay_kernel<__nv_bfloat16>, dim3(T), dim3(128), smem, stream, low, low_stride, (const __nv_bfloat16*)w2, bias, out, n, rank, 1.0f / tau, req_of_token);
     else
         return AIRUN_ERR_UNSUPPORTED;
     return airun_launch_status();
 }
 
-// The recurrence.  One block per (request, head, 32 value columns), 256 threads: a warp owns four
-// columns, and the eight lanes of a column own the key channels d = 32 * (i / 4) + 4 * part + i % 4
-// (i < NS: runs of four, so that q, k and the decay come from shared memory as float4), so a thread
-// keeps NS elements of the state in registers for the whole step.  The tokens of the request are
-// staged through shared memory a few at a time (q, k, log a per key channel, v per column) by
-// asynchronous copies into one of two stages, so that the next tokens are on their way while these are
-// used; exp(log a) is taken once per staged element.  Each thread updates its strip and the eight
-// partial sums of a column are added by shuffles.
+// The recurrence.  One block per (request, head, 32 value columns), 256 threads: a lane owns a column
+// and a warp owns NS key channels d = warp * NS + i, so a thread keeps NS elements of the state in
+// registers for the whole step, and q, k and the decay of a token are the same for all lanes of a warp:
+// they come from shared memory as float4 that every lane reads at one address (one access for the warp).
+// The tokens of the request are staged through shared memory a few at a time by asynchronous copies
+// (16 bytes each where the rows allow it) into one of two stages, so that the next tokens are on their way
+// while these are used.  Each warp leaves its partial sums over its key channels in shared
+// memory, and the eight partial sums of every (token, column) of the stage are added together, in warp
+// order, once the stage's tokens are through: nothing but the state itself chains one token to the next.
 #define GLA_COLS 32
+#define GLA_WARPS 8
 __device__ __forceinline__ void gla_cp4(float* smem, const float* gmem) {
     asm volatile("cp.async.ca.shared.global [%0], [%1], 4;" ::"r"((uint32_t)__cvta_generic_to_shared(smem)), "l"(gmem) : "memory");
+}
+__device__ __forceinline__ void gla_cp16(float* smem, const float* gmem) {
+    asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"((uint32_t)__cvta_generic_to_shared(smem)), "l"(gmem) : "memory");
 }
 template <int NS>
 __global__ __launch_bounds__(256) void gla_recurrent_kernel(
     const float* __restrict__ q, const float* __restrict__ k, const float* __restrict__ v, long long row_stride,
-    const float* __restrict__ log_decay, float* __restrict__ state, long long slot_stride,
+    const float* __restrict__ decay, float* __restrict__ state, long long slot_stride,
     const int32_t* __restrict__ cu_tokens, const int32_t* __restrict__ state_slots, int max_slots,
     float* __restrict__ out, int heads, int D, int Dv, float q_scale, int* __restrict__ err) {
     pdl_trigger();
     pdl_wait();
-    constexpr int DP = NS * 8;
+    constexpr int DP = NS * GLA_WARPS;
     constexpr int GLA_TT = NS >= 32 ? 4 : NS >= 16 ? 8 : 16;     // tokens of a stage (static shared memory stays under 48 KB)
     __shared__ __align__(16) float s_q[2][GLA_TT][DP], s_k[2][GLA_TT][DP], s_a[2][GLA_TT][DP], s_v[2][GLA_TT][GLA_COLS];
+    __shared__ float s_p[GLA_WARPS][GLA_TT][GLA_COLS];
     const int r = blockIdx.x, head = blockIdx.y, col0 = blockIdx.z * GLA_COLS;
     const int t0 = cu_tokens[r], n = cu_tokens[r + 1] - t0;
     if (n <= 0) return;
@@ -84,7 +90,7 @@ __global__ __launch_bounds__(256) void gla_recurrent_kernel(
         return;
     }
     const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
-    const int part = lane & 7, cw = warp * 4 + (lane >> 3), col = col0 + cw;
+    const int col = col0 + lane, d0 = warp * NS;
     const bool col_ok = col < Dv;
     // the padding beyond D and Dv is zero in both stages and is never copied into
     for (int e = threadIdx.x; e < 2 * GLA_TT * DP; e += 256) {
@@ -92,30 +98,46 @@ __global__ __launch_bounds__(256) void gla_recurrent_kernel(
     }
     for (int e = threadIdx.x; e < 2 * GLA_TT * GLA_COLS; e += 256) (&s_v[0][0][0])[e] = 0.0f;
     __syncthreads();
+    // 16-byte copies when every row begins on a 16-byte boundary
+    const bool vec = (D % 4 == 0) && (Dv % 4 == 0) && (row_stride % 4 == 0) &&
+                     ((((uintptr_t)q | (uintptr_t)k | (uintptr_t)v | (uintptr_t)decay) & 15) == 0);
     auto stage = [&](int base, int buf) {
         const int nt = min(GLA_TT, n - base);
-        for (int e = threadIdx.x; e < nt * D; e += 256) {
-            const int tt = e / D, d = e - tt * D;
-            const size_t row = (size_t)(t0 + base + tt);
-            gla_cp4(&s_q[buf][tt][d], q + row * row_stride + (size_t)head * D + d);
-            gla_cp4(&s_k[buf][tt][d], k + row * row_stride + (size_t)head * D + d);
-            gla_cp4(&s_a[buf][tt][d], log_decay + row * ((size_t)heads * D) + (size_t)head * D + d);
-        }
-        const int nc = min(GLA_COLS, Dv - col0);
-        for (int e = threadIdx.x; e < nt * nc; e += 256) {
-            const int tt = e / nc, c = e - tt * nc;
-            gla_cp4(&s_v[buf][tt][c], v + (size_t)(t0 + base + tt) * row_stride + (size_t)head * Dv + col0 + c);
+        if (vec) {
+            const int per = D / 4, nc4 = min(GLA_COLS, Dv - col0) / 4;
+            for (int e = threadIdx.x; e < nt * per; e += 256) {
+                const int tt = e / per, d = (e - tt * per) * 4;
+                const size_t row = (size_t)(t0 + base + tt);
+                gla_cp16(&s_q[buf][tt][d], q + row * row_stride + (size_t)head * D + d);
+                gla_cp16(&s_k[buf][tt][d], k + row * row_stride + (size_t)head * D + d);
+                gla_cp16(&s_a[buf][tt][d], decay + row * ((size_t)heads * D) + (size_t)head * D + d);
+            }
+            for (int e = threadIdx.x; e < nt * nc4; e += 256) {
+                const int tt = e / nc4, c = (e - tt * nc4) * 4;
+                gla_cp16(&s_v[buf][tt][c], v + (size_t)(t0 + base + tt) * row_stride + (size_t)head * Dv + col0 + c);
+            }
+        } else {
+            for (int e = threadIdx.x; e < nt * D; e += 256) {
+                const int tt = e / D, d = e - tt * D;
+                const size_t row = (size_t)(t0 + base + tt);
+                gla_cp4(&s_q[buf][tt][d], q + row * row_stride + (size_t)head * D + d);
+                gla_cp4(&s_k[buf][tt][d], k + row * row_stride + (size_t)head * D + d);
+                gla_cp4(&s_a[buf][tt][d], decay + row * ((size_t)heads * D) + (size_t)head * D + d);
+            }
+            const int nc = min(GLA_COLS, Dv - col0);
+            for (int e = threadIdx.x; e < nt * nc; e += 256) {
+                const int tt = e / nc, c = e - tt * nc;
+                gla_cp4(&s_v[buf][tt][c], v + (size_t)(t0 + base + tt) * row_stride + (size_t)head * Dv + col0 + c);
+            }
         }
         asm volatile("cp.async.commit_group;" ::: "memory");
     };
     stage(0, 0);
-    float* srow = state + (size_t)slot * slot_stride + ((size_t)head * Dv + (col_ok ? col : 0)) * D;
+    // the state of this head, [D][Dv]: the lanes of a warp read one row of it side by side
+    float* sbase = state + (size_t)slot * slot_stride + (size_t)head * D * Dv + (col_ok ? col : 0);
     float S[NS];
 #pragma unroll
-    for (int i = 0; i < NS; ++i) {
-        const int d = 32 * (i / 4) + 4 * part + (i % 4);
-        S[i] = (col_ok && d < D) ? srow[d] : 0.0f;
-    }
+    for (int i = 0; i < NS; ++i) S[i] = (col_ok && d0 + i < D) ? sbase[(size_t)(d0 + i) * Dv] : 0.0f;
     int it = 0;
     for (int base = 0; base < n; base += GLA_TT, ++it) {
         const int buf = it & 1, nt = min(GLA_TT, n - base);
@@ -126,44 +148,41 @@ __global__ __launch_bounds__(256) void gla_recurrent_kernel(
             asm volatile("cp.async.wait_group 0;" ::: "memory");
         }
         __syncthreads();
-        for (int e = threadIdx.x; e < nt * D; e += 256) {
-            const int tt = e / D, d = e - tt * D;
-            s_a[buf][tt][d] = expf(s_a[buf][tt][d]);
-        }
-        __syncthreads();
 #pragma unroll 4
         for (int tt = 0; tt < nt; ++tt) {
-            const float vj = s_v[buf][tt][cw];
-            float acc = 0.0f;
+            const float vj = s_v[buf][tt][lane];
+            float acc0 = 0.0f, acc1 = 0.0f;
 #pragma unroll
             for (int i4 = 0; i4 < NS / 4; ++i4) {
-                const int d = 32 * i4 + 4 * part;
-                const float4 a4 = *reinterpret_cast<const float4*>(&s_a[buf][tt][d]);
-                const float4 k4 = *reinterpret_cast<const float4*>(&s_k[buf][tt][d]);
-                const float4 q4 = *reinterpret_cast<const float4*>(&s_q[buf][tt][d]);
-                S[4 * i4 + 0] = fmaf(a4.x, S[4 * i4 + 0], k4.x * vj); acc = fmaf(S[4 * i4 + 0], q4.x, acc);
-                S[4 * i4 + 1] = fmaf(a4.y, S[4 * i4 + 1], k4.y * vj); acc = fmaf(S[4 * i4 + 1], q4.y, acc);
-                S[4 * i4 + 2] = fmaf(a4.z, S[4 * i4 + 2], k4.z * vj); acc = fmaf(S[4 * i4 + 2], q4.z, acc);
-                S[4 * i4 + 3] = fmaf(a4.w, S[4 * i4 + 3], k4.w * vj); acc = fmaf(S[4 * i4 + 3], q4.w, acc);
+                const float4 a4 = *reinterpret_cast<const float4*>(&s_a[buf][tt][d0 + 4 * i4]);
+                const float4 k4 = *reinterpret_cast<const float4*>(&s_k[buf][tt][d0 + 4 * i4]);
+                const float4 q4 = *reinterpret_cast<const float4*>(&s_q[buf][tt][d0 + 4 * i4]);
+                S[4 * i4 + 0] = fmaf(a4.x, S[4 * i4 + 0], k4.x * vj); acc0 = fmaf(S[4 * i4 + 0], q4.x, acc0);
+                S[4 * i4 + 1] = fmaf(a4.y, S[4 * i4 + 1], k4.y * vj); acc1 = fmaf(S[4 * i4 + 1], q4.y, acc1);
+                S[4 * i4 + 2] = fmaf(a4.z, S[4 * i4 + 2], k4.z * vj); acc0 = fmaf(S[4 * i4 + 2], q4.z, acc0);
+                S[4 * i4 + 3] = fmaf(a4.w, S[4 * i4 + 3], k4.w * vj); acc1 = fmaf(S[4 * i4 + 3], q4.w, acc1);
             }
-            acc += __shfl_xor_sync(0xffffffffu, acc, 1);
-            acc += __shfl_xor_sync(0xffffffffu, acc, 2);
-            acc += __shfl_xor_sync(0xffffffffu, acc, 4);
-            if (part == 0 && col_ok) out[(size_t)(t0 + base + tt) * ((size_t)heads * Dv) + (size_t)head * Dv + col] = acc * q_scale;
+            s_p[warp][tt][lane] = acc0 + acc1;
+        }
+        __syncthreads();
+        for (int e = threadIdx.x; e < nt * GLA_COLS; e += 256) {
+            const int tt = e / GLA_COLS, c = e - tt * GLA_COLS;
+            float o = 0.0f;
+#pragma unroll
+            for (int w = 0; w < GLA_WARPS; ++w) o += s_p[w][tt][c];
+            if (col0 + c < Dv) out[(size_t)(t0 + base + tt) * ((size_t)heads * Dv) + (size_t)head * Dv + col0 + c] = o * q_scale;
         }
         __syncthreads();
     }
     if (col_ok) {
 #pragma unroll
-        for (int i = 0; i < NS; ++i) {
-            const int d = 32 * (i / 4) + 4 * part + (i % 4);
-            if (d < D) srow[d] = S[i];
-        }
+        for (int i = 0; i < NS; ++i)
+            if (d0 + i < D) sbase[(size_t)(d0 + i) * Dv] = S[i];
     }
 }
 
 AIRUN_EXPORT int airun_gla_recurrent(const float* q, const float* k, const float* v, long long row_stride,
-                                     const float* log_decay, float* state, long long slot_stride, int max_slots,
+                                     const float* decay, float* state, long long slot_stride, int max_slots,
                                      const int32_t* cu_tokens, const int32_t* state_slots, int num_reqs,
                                      float* out, int heads, int D, int Dv, float q_scale, int* err, cudaStream_t stream) {
     if (num_reqs < 0 || heads <= 0 || D <= 0 || D > 256 || Dv <= 0 || !state || !cu_tokens || !state_slots || !err ||
@@ -173,7 +192,7 @@ AIRUN_EXPORT int airun_gla_recurrent(const float* q, const float* k, const float
     const int tiles = ceil_div_i(Dv, GLA_COLS);
     if (tiles > 65535) return AIRUN_ERR_ARG;
     dim3 grid(num_reqs, heads, tiles);
-#define GLA_LAUNCH(NS) airun_launch(gla_recurrent_kernel<NS>, grid, dim3(256), 0, stream, q, k, v, row_stride, log_decay, state, \
+#define GLA_LAUNCH(NS) airun_launch(gla_recurrent_kernel<NS>, grid, dim3(256), 0, stream, q, k, v, row_stride, decay, state, \
         slot_stride, cu_tokens, state_slots, max_slots, out, heads, D, Dv, q_scale, err)
     if (D <= 32) GLA_LAUNCH(4);
     else if (D <= 64) GLA_LAUNCH(8);

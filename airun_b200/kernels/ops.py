@@ -248,9 +248,9 @@ def _row_stride(t: torch.Tensor) -> int:
     return t.stride(0) if t.shape[0] > 1 else max(t.shape[1], t.stride(0))
 
 
-def gla_log_decay(low: torch.Tensor, w2: torch.Tensor, bias: Optional[torch.Tensor], tau: float, out: torch.Tensor,
+def gla_decay(low: torch.Tensor, w2: torch.Tensor, bias: Optional[torch.Tensor], tau: float, out: torch.Tensor,
                   req_of_token: torch.Tensor) -> None:
-    """out[t, c] = logsigmoid(bias[c] + low[t] . w2[c]) / tau: the logarithm of the decay sigmoid(z)^(1/tau)."""
+    """out[t, c] = exp(logsigmoid(bias[c] + low[t] . w2[c]) / tau): the decay sigmoid(z)^(1/tau), in (0, 1)."""
     _cuda(low, w2, bias, out, req_of_token)
     _rows_f32(low, "low")
     T, rank = low.shape
@@ -260,29 +260,29 @@ def gla_log_decay(low: torch.Tensor, w2: torch.Tensor, bias: Optional[torch.Tens
         _need(bias.dtype == torch.float32 and tuple(bias.shape) == (n,) and bias.is_contiguous(), "bias must be float32 [n]")
     _need(out.dtype == torch.float32 and tuple(out.shape) == (T, n) and out.is_contiguous(), "out must be float32 [T, n]")
     _need(req_of_token.dtype == torch.int32 and req_of_token.shape[0] >= T, "req_of_token must be int32 [T]")
-    f = _fn("linear_attention", "airun_gla_log_decay",
+    f = _fn("linear_attention", "airun_gla_decay",
             [c_void_p, c_longlong, c_void_p, c_int, c_void_p, c_void_p, c_int, c_int, c_int, c_float, c_void_p, c_void_p])
     _check(f(_p(low), _row_stride(low), _p(w2), _dt(w2), _p(bias), _p(out), T, n, rank, float(tau), _p(req_of_token),
-             _stream()), "gla_log_decay")
+             _stream()), "gla_decay")
 
 
-def gla_recurrent(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, log_decay: torch.Tensor, state: torch.Tensor,
+def gla_recurrent(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, decay: torch.Tensor, state: torch.Tensor,
                   cu_tokens: torch.Tensor, state_slots: torch.Tensor, num_reqs: int, out: torch.Tensor,
                   heads: int, D: int, Dv: int, q_scale: float, err: torch.Tensor) -> None:
     """The recurrence S <- diag(a) S + k v^T, o = S^T q * q_scale for the tokens of every request in order.
     ``q``, ``k`` [T, heads*D] and ``v`` [T, heads*Dv] are float32 column slices of ONE buffer (equal row strides);
-    ``state`` is [slots, heads, Dv, D] float32 and is updated in place; ``out`` float32 [T, heads*Dv]."""
-    _cuda(q, k, v, log_decay, state, cu_tokens, state_slots, out, err)
+    ``state`` is [slots, heads, D, Dv] float32 and is updated in place; ``out`` float32 [T, heads*Dv]."""
+    _cuda(q, k, v, decay, state, cu_tokens, state_slots, out, err)
     for t, w, name in ((q, heads * D, "q"), (k, heads * D, "k"), (v, heads * Dv, "v")):
         _rows_f32(t, name)
         _need(t.shape[1] == w, f"{name} must have {w} columns")
     T = q.shape[0]
     _need(_row_stride(q) == _row_stride(k) or T <= 1, "q, k and v must share a row stride")
     _need(k.stride(0) == v.stride(0) or T <= 1, "q, k and v must share a row stride")
-    _need(log_decay.dtype == torch.float32 and tuple(log_decay.shape) == (T, heads * D) and log_decay.is_contiguous(),
-          "log_decay must be float32 [T, heads*D]")
-    _need(state.dtype == torch.float32 and state.dim() == 4 and tuple(state.shape[1:]) == (heads, Dv, D)
-          and state[0].is_contiguous(), "state must be float32 [slots, heads, Dv, D]")
+    _need(decay.dtype == torch.float32 and tuple(decay.shape) == (T, heads * D) and decay.is_contiguous(),
+          "decay must be float32 [T, heads*D]")
+    _need(state.dtype == torch.float32 and state.dim() == 4 and tuple(state.shape[1:]) == (heads, D, Dv)
+          and state[0].is_contiguous(), "state must be float32 [slots, heads, D, Dv]")
     _need(out.dtype == torch.float32 and tuple(out.shape) == (T, heads * Dv) and out.is_contiguous(), "out must be float32 [T, heads*Dv]")
     _need(cu_tokens.dtype == torch.int32 and cu_tokens.numel() >= num_reqs + 1 and state_slots.dtype == torch.int32
           and state_slots.numel() >= num_reqs, "cu_tokens / state_slots must be int32 [R + 1] / [R]")
@@ -291,7 +291,7 @@ def gla_recurrent(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, log_decay: 
     f = _fn("linear_attention", "airun_gla_recurrent",
             [c_void_p, c_void_p, c_void_p, c_longlong, c_void_p, c_void_p, c_longlong, c_int, c_void_p, c_void_p, c_int,
              c_void_p, c_int, c_int, c_int, c_float, c_void_p, c_void_p])
-    _check(f(_p(q), _p(k), _p(v), stride, _p(log_decay), _p(state), state.stride(0), state.shape[0], _p(cu_tokens),
+    _check(f(_p(q), _p(k), _p(v), stride, _p(decay), _p(state), state.stride(0), state.shape[0], _p(cu_tokens),
              _p(state_slots), int(num_reqs), _p(out), heads, D, Dv, float(q_scale), _p(err), _stream()), "gla_recurrent")
 
 

@@ -69,7 +69,7 @@ class GatedLinearAttention(Mixer):
 
     # ---- cache ----
     def cache_spec(self):
-        return StateSpec((self.nh, self.Dv, self.D), torch.float32)
+        return StateSpec((self.nh, self.D, self.Dv), torch.float32)
 
     # ---- compute ----
     def forward_core(self, ctx, h: torch.Tensor, act: torch.Tensor, cache) -> None:
@@ -79,10 +79,10 @@ class GatedLinearAttention(Mixer):
         linear(ctx, h, self.w_in, proj)
         q, k, v = proj[:, :kd], proj[:, kd:2 * kd], proj[:, 2 * kd:2 * kd + vd]
         gate, low = proj[:, 2 * kd + vd:2 * kd + 2 * vd], proj[:, 2 * kd + 2 * vd:]
-        log_decay = ws.alloc((T, kd), torch.float32)
-        ops.gla_log_decay(low, self.w_decay, self.decay_bias, self.tau, log_decay, ctx.req_of_token)
+        decay = ws.alloc((T, kd), torch.float32)
+        ops.gla_decay(low, self.w_decay, self.decay_bias, self.tau, decay, ctx.req_of_token)
         o = ws.alloc((T, vd), torch.float32)
-        ops.gla_recurrent(q, k, v, log_decay, cache.state, ctx.cu_tokens, ctx.state_slots, ctx.num_reqs, o,
+        ops.gla_recurrent(q, k, v, decay, cache.state, ctx.cu_tokens, ctx.state_slots, ctx.num_reqs, o,
                           self.nh, self.D, self.Dv, self.q_scale, ctx.err)
         ops.gla_out_gate(o, gate, self.norm_w, self.eps, act, self.nh, self.Dv, ctx.req_of_token)
 

@@ -600,7 +600,7 @@ def workload_vedizen(a) -> int:
                 kinds["norm (dynamic tanh)"] = (ops, "dyt_norm", lambda t: 7 * t * W * 14.0, "hbm")
                 kinds["q/k/v bias + cache write"] = (ops, "qkv_bias_store", lambda t: n_att * t * ((H + G) * 128 + G * 128) * 6.0, "hbm")
                 kinds["differential attention"] = (fast, "diff_attention_bf16", None, "mixed")
-                kinds["linear attention: decay"] = (ops, "gla_log_decay", lambda t: n_gla * t * H * 64 * 4.0, "hbm")
+                kinds["linear attention: decay"] = (ops, "gla_decay", lambda t: n_gla * t * H * 64 * 4.0, "hbm")
                 kinds["linear attention: recurrence"] = (ops, "gla_recurrent", None, "mixed")
                 kinds["linear attention: norm and gate"] = (ops, "gla_out_gate", lambda t: n_gla * t * H * 128 * 10.0, "hbm")
                 kinds["gate/up product + gated unit"] = (fast, "linear_glu_clamped_bf16", lambda t: 6 * 2.0 * t * W * 2 * F, "tensor")
