@@ -54,6 +54,7 @@ struct DamParams {
     float scale, cap, lambda, eps, out_scale;
     int chunk, window;
     int skip_single;              // requests that bring ONE token are left to the decode kernel
+    int head_split;               // decode kernel: CTAs that share the heads of one KV head among them
     int* err;
 };
 
@@ -324,7 +325,8 @@ __global__ __launch_bounds__(256, (G <= 2 ? 2 : 1)) void diff_attention_decode_k
     pdl_trigger();
     pdl_wait();
     extern __shared__ __align__(16) unsigned char dam_smem[];
-    const int r = blockIdx.y, kvh = blockIdx.x;
+    const int r = blockIdx.y, kvh = blockIdx.x / p.head_split;
+    const int head0 = kvh * (G * p.head_split) + (blockIdx.x % p.head_split) * G;      // first of this CTA's G query heads
     const int t = p.cu_tokens[r];
     if (p.cu_tokens[r + 1] - t != 1) return;
     const int pos = p.context_lens[r] - 1;
@@ -337,7 +339,7 @@ __global__ __launch_bounds__(256, (G <= 2 ? 2 : 1)) void diff_attention_decode_k
 #pragma unroll
     for (int g = 0; g < G; ++g) {
         uint4 raw = make_uint4(0u, 0u, 0u, 0u);
-        if (k_on) raw = *reinterpret_cast<const uint4*>(p.q + ((size_t)t * p.nh + kvh * G + g) * kd + li * 8);
+        if (k_on) raw = *reinterpret_cast<const uint4*>(p.q + ((size_t)t * p.nh + head0 + g) * kd + li * 8);
         const __nv_bfloat162* h2 = reinterpret_cast<const __nv_bfloat162*>(&raw);
 #pragma unroll
         for (int i = 0; i < 4; ++i) { const float2 f = __bfloat1622float2(h2[i]); qf[g][2 * i] = f.x; qf[g][2 * i + 1] = f.y; }
@@ -452,7 +454,7 @@ __global__ __launch_bounds__(256, (G <= 2 ? 2 : 1)) void diff_attention_decode_k
     }
     __syncthreads();
     if (warp >= G) return;
-    const int g = warp, head = kvh * G + g;
+    const int g = warp, head = head0 + g;
     float o[8];
 #pragma unroll
     for (int i = 0; i < 8; ++i) o[i] = 0.0f;
@@ -506,7 +508,7 @@ static int dad_launch(const DamParams& p, cudaStream_t stream) {
         cudaError_t e = cudaFuncSetAttribute(diff_attention_decode_kernel<G, GS>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
         if (e != cudaSuccess) return (int)e;
     }
-    airun_launch(diff_attention_decode_kernel<G, GS>, dim3(p.nkv, p.num_reqs), dim3(256), smem, stream, p);
+    airun_launch(diff_attention_decode_kernel<G, GS>, dim3(p.nkv * p.head_split, p.num_reqs), dim3(256), smem, stream, p);
     return airun_launch_status();
 }
 
@@ -546,7 +548,7 @@ AIRUN_EXPORT int airun_diff_attention_mma(const void* q, void* out, long long ou
     p.pool = (const __nv_bfloat16*)pool; p.block_table = block_table; p.max_blocks = max_blocks;
     p.cu_tokens = cu_tokens; p.context_lens = context_lens; p.num_reqs = num_reqs; p.num_pages = num_pages;
     p.page_size = page_size; p.nh = nh; p.nkv = nkv; p.D = D; p.Dv = Dv; p.scale = scale; p.cap = cap;
-    p.lambda = lambda; p.eps = eps; p.out_scale = out_scale; p.chunk = chunk; p.window = window; p.skip_single = skip_single; p.err = err;
+    p.lambda = lambda; p.eps = eps; p.out_scale = out_scale; p.chunk = chunk; p.window = window; p.skip_single = skip_single; p.head_split = 1; p.err = err;
     const int dp = D <= 32 ? 32 : D <= 64 ? 64 : 128, dvp = Dv <= 32 ? 32 : Dv <= 64 ? 64 : 128;
 #define DAM_CASE(A, B) if (dp == A && dvp == B) return dam_launch<A, B>(p, max_tiles, stream)
     DAM_CASE(32, 32); DAM_CASE(32, 64); DAM_CASE(32, 128);
@@ -573,10 +575,13 @@ AIRUN_EXPORT int airun_diff_attention_decode(const void* q, void* out, long long
     p.cu_tokens = cu_tokens; p.context_lens = context_lens; p.num_reqs = num_reqs; p.num_pages = num_pages;
     p.page_size = page_size; p.nh = nh; p.nkv = nkv; p.D = D; p.Dv = Dv; p.scale = scale; p.cap = cap;
     p.lambda = lambda; p.eps = eps; p.out_scale = out_scale; p.chunk = chunk; p.window = window; p.skip_single = 0; p.err = err;
-    const int G = nh / nkv, width = 2 * D > Dv ? 2 * D : Dv, gs = width <= 64 ? 8 : width <= 128 ? 16 : 32;
+    // groups of four or eight heads run as CTAs of two heads each (two such CTAs fit an SM at once; the keys they
+    // share come from the L2 cache for all but the first)
+    const int Gall = nh / nkv, G = Gall > 2 ? 2 : Gall;
+    p.head_split = Gall / G;
+    const int width = 2 * D > Dv ? 2 * D : Dv, gs = width <= 64 ? 8 : width <= 128 ? 16 : 32;
 #define DAD_CASE(A, B) if (G == A && gs == B) return dad_launch<A, B>(p, stream)
     DAD_CASE(1, 8); DAD_CASE(1, 16); DAD_CASE(1, 32); DAD_CASE(2, 8); DAD_CASE(2, 16); DAD_CASE(2, 32);
-    DAD_CASE(4, 8); DAD_CASE(4, 16); DAD_CASE(4, 32); DAD_CASE(8, 8); DAD_CASE(8, 16); DAD_CASE(8, 32);
 #undef DAD_CASE
     return AIRUN_ERR_UNSUPPORTED;
 }

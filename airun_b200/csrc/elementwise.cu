@@ -414,6 +414,20 @@ __global__ void dyt_norm_kernel(float* __restrict__ x, const float* __restrict__
     float* xr = x + (size_t)src * n;
     const float* dr = delta ? delta + (size_t)src * n : nullptr;
     TOut* outr = out + (size_t)r * n;
+    if (n % 4 == 0) {                    // rows of float4 (the row pointers are then 16-byte aligned like their bases)
+        for (int i = blockIdx.y * blockDim.x + threadIdx.x; i < n / 4; i += gridDim.y * blockDim.x) {
+            float4 v = reinterpret_cast<const float4*>(xr)[i];
+            if (dr) { const float4 d = reinterpret_cast<const float4*>(dr)[i]; v.x += d.x; v.y += d.y; v.z += d.z; v.w += d.w; }
+            if (vec) { const float4 d = reinterpret_cast<const float4*>(vec)[i]; v.x += d.x; v.y += d.y; v.z += d.z; v.w += d.w; }
+            if (write_back) reinterpret_cast<float4*>(xr)[i] = v;
+            const float4 ww = reinterpret_cast<const float4*>(w)[i], bb = reinterpret_cast<const float4*>(b)[i];
+            outr[4 * i + 0] = from_f32<TOut>(fmaf(tanhf(a * v.x), ww.x, bb.x));
+            outr[4 * i + 1] = from_f32<TOut>(fmaf(tanhf(a * v.y), ww.y, bb.y));
+            outr[4 * i + 2] = from_f32<TOut>(fmaf(tanhf(a * v.z), ww.z, bb.z));
+            outr[4 * i + 3] = from_f32<TOut>(fmaf(tanhf(a * v.w), ww.w, bb.w));
+        }
+        return;
+    }
     for (int i = blockIdx.y * blockDim.x + threadIdx.x; i < n; i += gridDim.y * blockDim.x) {
         float v = xr[i];
         if (dr) v += dr[i];
@@ -429,7 +443,8 @@ AIRUN_EXPORT int airun_dyt_norm(float* x, const float* delta, const float* vec, 
     if (n_rows < 0 || n <= 0 || !alpha || !w || !b) return AIRUN_ERR_ARG;
     if (n_rows == 0) return AIRUN_OK;
     const int threads = 256;
-    dim3 grid(n_rows, min(ceil_div_i(n, threads), 64));
+    if (n % 4 == 0 && ((((uintptr_t)x | (uintptr_t)delta | (uintptr_t)vec | (uintptr_t)w | (uintptr_t)b) & 15) != 0)) return AIRUN_ERR_ARG;
+    dim3 grid(n_rows, min(ceil_div_i(n % 4 == 0 ? n / 4 : n, threads), 64));
     if (out_dtype == AIRUN_DT_F32)
         airun_launch(dyt_norm_kernel<float>, grid, dim3(threads), 0, stream, x, delta, vec, alpha, w, b, (float*)out, rows, n, write_back);
     else if (out_dtype == AIRUN_DT_BF16)

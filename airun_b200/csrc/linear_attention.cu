@@ -16,37 +16,54 @@
 #include "common.cuh"
 
 // a[t][c] = exp(logsigmoid(bias[c] + sum_j low[t][j] * w2[c][j]) / tau) for c < n (= heads * D).
+#define DECAY_TOKENS 8        // tokens of one block: a row of w2 is read once for all of them
 template <typename TW>
-__global__ void decay_kernel(const float* __restrict__ low, long long low_stride, const TW* __restrict__ w2,
-                                 const float* __restrict__ bias, float* __restrict__ out, int n, int rank,
-                                 float inv_tau, const int32_t* __restrict__ req_of_token) {
+__global__ __launch_bounds__(128) void decay_kernel(const float* __restrict__ low, long long low_stride, const TW* __restrict__ w2,
+                                                    const float* __restrict__ bias, float* __restrict__ out, int T, int n, int rank,
+                                                    float inv_tau, const int32_t* __restrict__ req_of_token) {
     pdl_trigger();
     pdl_wait();
-    extern __shared__ float s_low[];
-    const int t = blockIdx.x;
-    if (req_of_token[t] < 0) return;
-    for (int j = threadIdx.x; j < rank; j += blockDim.x) s_low[j] = low[(size_t)t * low_stride + j];
+    extern __shared__ float s_low[];                       // [DECAY_TOKENS][rank]
+    const int t0 = blockIdx.x * DECAY_TOKENS, nt = min(DECAY_TOKENS, T - t0);
+    for (int e = threadIdx.x; e < nt * rank; e += blockDim.x) {
+        const int tk = e / rank, j = e - tk * rank;
+        s_low[e] = low[(size_t)(t0 + tk) * low_stride + j];
+    }
     __syncthreads();
-    for (int c = threadIdx.x; c < n; c += blockDim.x) {
-        float z = bias ? bias[c] : 0.0f;
+    const int c = blockIdx.y * blockDim.x + threadIdx.x;       // a channel a thread
+    if (c < n) {
+        float z[DECAY_TOKENS];
+        const float b = bias ? bias[c] : 0.0f;
+#pragma unroll
+        for (int tk = 0; tk < DECAY_TOKENS; ++tk) z[tk] = b;
         const TW* wr = w2 + (size_t)c * rank;
-        for (int j = 0; j < rank; ++j) z = fmaf(s_low[j], to_f32<TW>(wr[j]), z);
-        // logsigmoid(z) = min(z, 0) - log(1 + exp(-|z|))
-        const float ls = fminf(z, 0.0f) - log1pf(expf(-fabsf(z)));
-        out[(size_t)t * n + c] = expf(ls * inv_tau);
+        for (int j = 0; j < rank; ++j) {
+            const float w = to_f32<TW>(wr[j]);
+#pragma unroll
+            for (int tk = 0; tk < DECAY_TOKENS; ++tk)
+                if (tk < nt) z[tk] = fmaf(s_low[tk * rank + j], w, z[tk]);
+        }
+#pragma unroll
+        for (int tk = 0; tk < DECAY_TOKENS; ++tk) {
+            if (tk >= nt || req_of_token[t0 + tk] < 0) continue;
+            // logsigmoid(z) = min(z, 0) - log(1 + exp(-|z|))
+            const float ls = fminf(z[tk], 0.0f) - log1pf(expf(-fabsf(z[tk])));
+            out[(size_t)(t0 + tk) * n + c] = expf(ls * inv_tau);
+        }
     }
 }
 
 AIRUN_EXPORT int airun_gla_decay(const float* low, long long low_stride, const void* w2, int w_dtype, const float* bias,
                                      float* out, int T, int n, int rank, float tau, const int32_t* req_of_token,
                                      cudaStream_t stream) {
-    if (T < 0 || n <= 0 || rank <= 0 || rank > 8192 || !(tau > 0.0f) || !req_of_token) return AIRUN_ERR_ARG;
+    if (T < 0 || n <= 0 || n > 65535 * 128 || rank <= 0 || rank > 1024 || !(tau > 0.0f) || !req_of_token) return AIRUN_ERR_ARG;
     if (T == 0) return AIRUN_OK;
-    const size_t smem = (size_t)rank * sizeof(float);
+    const size_t smem = (size_t)DECAY_TOKENS * rank * sizeof(float);
+    const int blocks = ceil_div_i(T, DECAY_TOKENS);
     if (w_dtype == AIRUN_DT_F32)
-        airun_launch(decay_kernel<float>, dim3(T), dim3(128), smem, stream, low, low_stride, (const float*)w2, bias, out, n, rank, 1.0f / tau, req_of_token);
+        airun_launch(decay_kernel<float>, dim3(blocks, ceil_div_i(n, 128)), dim3(128), smem, stream, low, low_stride, (const float*)w2, bias, out, T, n, rank, 1.0f / tau, req_of_token);
     else if (w_dtype == AIRUN_DT_BF16)
-        airun_launch(decay_kernel<__nv_bfloat16>, dim3(T), dim3(128), smem, stream, low, low_stride, (const __nv_bfloat16*)w2, bias, out, n, rank, 1.0f / tau, req_of_token);
+        airun_launch(decay_kernel<__nv_bfloat16>, dim3(blocks, ceil_div_i(n, 128)), dim3(128), smem, stream, low, low_stride, (const __nv_bfloat16*)w2, bias, out, T, n, rank, 1.0f / tau, req_of_token);
     else
         return AIRUN_ERR_UNSUPPORTED;
     return airun_launch_status();
@@ -215,12 +232,31 @@ __global__ __launch_bounds__(128) void out_gate_kernel(const float* __restrict__
     const int t = unit / heads, h = unit - t * heads;
     if (req_of_token[t] < 0) return;
     const float* orow = o + ((size_t)t * heads + h) * Dv;
+    const float* grow = gate + (size_t)t * gate_stride + (size_t)h * Dv;
+    TOut* dst = out + (size_t)t * out_stride + (size_t)h * Dv;
+    if (Dv <= 128 && Dv % 4 == 0 && ((((uintptr_t)orow | (uintptr_t)grow) & 15) == 0)) {
+        // a lane takes four values: both loads are issued before anything is used
+        const bool on = lane * 4 < Dv;
+        float4 ov = make_float4(0.0f, 0.0f, 0.0f, 0.0f), gv = ov, wv = make_float4(1.0f, 1.0f, 1.0f, 1.0f);
+        if (on) {
+            ov = *reinterpret_cast<const float4*>(orow + lane * 4);
+            gv = *reinterpret_cast<const float4*>(grow + lane * 4);
+            if (w) wv = make_float4(w[lane * 4], w[lane * 4 + 1], w[lane * 4 + 2], w[lane * 4 + 3]);
+        }
+        const float ss4 = warp_sum(ov.x * ov.x + ov.y * ov.y + ov.z * ov.z + ov.w * ov.w);
+        const float inv4 = 1.0f / sqrtf(ss4 / (float)Dv + eps);
+        if (on) {
+            dst[lane * 4 + 0] = from_f32<TOut>(ov.x * inv4 * wv.x * (gv.x / (1.0f + expf(-gv.x))));
+            dst[lane * 4 + 1] = from_f32<TOut>(ov.y * inv4 * wv.y * (gv.y / (1.0f + expf(-gv.y))));
+            dst[lane * 4 + 2] = from_f32<TOut>(ov.z * inv4 * wv.z * (gv.z / (1.0f + expf(-gv.z))));
+            dst[lane * 4 + 3] = from_f32<TOut>(ov.w * inv4 * wv.w * (gv.w / (1.0f + expf(-gv.w))));
+        }
+        return;
+    }
     float ss = 0.0f;
     for (int j = lane; j < Dv; j += 32) ss = fmaf(orow[j], orow[j], ss);
     ss = warp_sum(ss);
     const float inv = 1.0f / sqrtf(ss / (float)Dv + eps);
-    const float* grow = gate + (size_t)t * gate_stride + (size_t)h * Dv;
-    TOut* dst = out + (size_t)t * out_stride + (size_t)h * Dv;
     for (int j = lane; j < Dv; j += 32) {
         const float g = grow[j];
         dst[j] = from_f32<TOut>(orow[j] * inv * (w ? w[j] : 1.0f) * (g / (1.0f + expf(-g))));
