@@ -1,4 +1,4 @@
-// Differential attention of prompt portions and decoded tokens on the tensor cores (mma.sync m16n8k16,
+// Differential attention of prompt portions and of single decoded tokens on the tensor cores (mma.sync m16n8k16,
 // bfloat16 operands, float32 accumulation).  The formulas and the page layout are those of
 // diff_attention.cu, its plain twin; this file only computes them tile by tile.
 //
@@ -31,10 +31,6 @@ __device__ __forceinline__ uint32_t pack_bf16(float lo, float hi) {
     __nv_bfloat162 h = __floats2bfloat162_rn(lo, hi);
     return *reinterpret_cast<uint32_t*>(&h);
 }
-// tanh through one exponential: exact to a few units of float32's last place away from 0, absolute error
-// about 1e-7 near it
-__device__ __forceinline__ float tanh_exp(float y) { return 1.0f - __fdividef(2.0f, __expf(2.0f * y) + 1.0f); }
-
 __device__ __forceinline__ void cp_async16(void* smem, const void* gmem) {
     asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"((uint32_t)__cvta_generic_to_shared(smem)), "l"(gmem) : "memory");
 }
@@ -53,8 +49,7 @@ struct DamParams {
     int num_reqs, num_pages, page_size, nh, nkv, D, Dv;
     float scale, cap, lambda, eps, out_scale;
     int chunk, window;
-    int skip_single;              // requests that bring ONE token are left to the decode kernel
-    int head_split;               // decode kernel: CTAs that share the heads of one KV head among them
+    int skip_single;              // requests that bring ONE token are left to the kernel for single tokens
     int* err;
 };
 
@@ -135,10 +130,35 @@ __global__ __launch_bounds__(128) void diff_attention_mma_kernel(const DamParams
     // K and V rows of up to 64 keys from kbase on into stage `buf` (rows beyond the last key keep what they held:
     // they are masked).  With 16-byte rows the copies are asynchronous and the next tile is on its way while
     // this one is used.
+    // when the 16-byte pieces of a key's rows divide the CTA's threads evenly and pages are a power of two, each thread
+    // owns one piece (reg_*: where it lies in the page and in shared memory) for every key it copies
+    const int reg_lp = max(1, kd / 8 + Dv / 8);
+    const bool regular = vec && reg_lp <= 128 && 128 % reg_lp == 0 && (p.page_size & (p.page_size - 1)) == 0;
+    const int ps_shift = __ffs(p.page_size) - 1;
+    const int reg_u = tid % reg_lp, reg_key0 = tid / reg_lp, reg_step = 128 / reg_lp;
+    const bool reg_is_k = reg_u < kd / 8;
+    const int reg_c = reg_is_k ? reg_u * 8 : (reg_u - kd / 8) * 8;
+    const int reg_dst = reg_is_k ? (reg_c / D) * DP + reg_c % D : reg_c;
+    const int reg_stride = reg_is_k ? QS : VS, reg_row = reg_is_k ? kd : Dv;
+    const size_t reg_src = reg_is_k ? (size_t)kvh * p.page_size * kd + reg_c
+                                    : (size_t)p.nkv * p.page_size * kd + (size_t)kvh * p.page_size * Dv + reg_c;
     auto load_tile = [&](int kbase, int buf) {
         __nv_bfloat16* Ks = Ks0 + buf * DAM_KEYS * QS;
         __nv_bfloat16* Vs = Vs0 + buf * DAM_KEYS * VS;
         const int nk = min(DAM_KEYS, hi - kbase + 1);
+        if (regular) {
+            // a thread keeps its 16-byte column of the key (or value) row and walks the keys: nothing but the page
+            // lookup is worked out per copy
+            __nv_bfloat16* dst = (reg_is_k ? Ks : Vs) + reg_dst;
+            for (int key = reg_key0; key < nk; key += reg_step) {
+                const int j = kbase + key, blk = j >> ps_shift;
+                const int page = blk < p.max_blocks ? bt[blk] : -1;
+                if (page < 0 || page >= p.num_pages) { bad = true; continue; }
+                cp_async16(dst + key * reg_stride, p.pool + (size_t)page * page_elems + reg_src + (size_t)(j & (p.page_size - 1)) * reg_row);
+            }
+            cp_async_commit();
+            return;
+        }
         const int perk = vec ? kd / 8 : kd, perv = vec ? Dv / 8 : Dv;
         for (int e = tid; e < nk * (perk + perv); e += 128) {
             const int key = e / (perk + perv), u = e - key * (perk + perv);
@@ -312,213 +332,6 @@ __global__ __launch_bounds__(128) void diff_attention_mma_kernel(const DamParams
 }
 
 // ---------------------------------------------------------------------------------------------------------
-// Single decoded tokens.  One CTA (8 warps) per (request that brings ONE token, KV head): all G query heads
-// of the group, both maps, share every key and value row that is read.  A group of GS lanes takes one key at a
-// time (a lane holds 8 consecutive elements of the key row and of the value row, read with one 16-byte load each);
-// the 256 / GS groups of the CTA walk the visible keys side by side, each with a running maximum, sum and value
-// accumulator per (head, map) in float32, and are merged at the end: first inside a warp by shuffles, then across
-// the warps through shared memory, in a fixed order.  Then o = a_1 - lambda * a_2 is normed per head and written.
-// D and Dv must be multiples of 8 (16-byte rows) with 2*D and Dv up to 8*GS; otherwise the tile kernel above
-// takes the token.
-template <int G, int GS>
-__global__ __launch_bounds__(256, (G <= 2 ? 2 : 1)) void diff_attention_decode_kernel(const DamParams p) {
-    pdl_trigger();
-    pdl_wait();
-    extern __shared__ __align__(16) unsigned char dam_smem[];
-    const int r = blockIdx.y, kvh = blockIdx.x / p.head_split;
-    const int head0 = kvh * (G * p.head_split) + (blockIdx.x % p.head_split) * G;      // first of this CTA's G query heads
-    const int t = p.cu_tokens[r];
-    if (p.cu_tokens[r + 1] - t != 1) return;
-    const int pos = p.context_lens[r] - 1;
-    const int D = p.D, Dv = p.Dv, kd = 2 * D;
-    const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31, li = tid % GS, worker = tid / GS;
-    constexpr int WORKERS = 256 / GS;
-    const bool k_on = li * 8 < kd, v_on = li * 8 < Dv;
-    const int my_map = li * 8 >= D ? 1 : 0;
-    float qf[G][8], acc[G][2][8], mx[G][2], sm[G][2];
-#pragma unroll
-    for (int g = 0; g < G; ++g) {
-        uint4 raw = make_uint4(0u, 0u, 0u, 0u);
-        if (k_on) raw = *reinterpret_cast<const uint4*>(p.q + ((size_t)t * p.nh + head0 + g) * kd + li * 8);
-        const __nv_bfloat162* h2 = reinterpret_cast<const __nv_bfloat162*>(&raw);
-#pragma unroll
-        for (int i = 0; i < 4; ++i) { const float2 f = __bfloat1622float2(h2[i]); qf[g][2 * i] = f.x; qf[g][2 * i + 1] = f.y; }
-#pragma unroll
-        for (int m = 0; m < 2; ++m) {
-            mx[g][m] = -INFINITY; sm[g][m] = 0.0f;
-#pragma unroll
-            for (int i = 0; i < 8; ++i) acc[g][m][i] = 0.0f;
-        }
-    }
-    int lo = p.chunk > 0 ? (pos / p.chunk) * p.chunk : 0;
-    if (p.window > 0) lo = max(lo, pos - p.window + 1);
-    const size_t page_elems = (size_t)p.nkv * p.page_size * (kd + Dv);
-    const int32_t* bt = p.block_table + (size_t)r * p.max_blocks;
-    const float inv_cap = p.cap > 0.0f ? 1.0f / p.cap : 0.0f;
-    bool bad = false;
-    // every group makes the same number of rounds (the shuffles below take whole warps); a group without a
-    // key in the last round reads nothing and leaves its sums alone
-    const int rounds = (pos - lo + WORKERS) / WORKERS;
-    constexpr int U = 4;                                   // rounds whose loads are issued before the first is used
-    for (int round0 = 0; round0 < rounds; round0 += U) {
-        uint4 kraw[U], vraw[U];
-        bool valid[U];
-#pragma unroll
-        for (int u = 0; u < U; ++u) {
-            const int j = lo + (round0 + u) * WORKERS + worker;
-            valid[u] = round0 + u < rounds && j <= pos;
-            const int blk = j / p.page_size;
-            const int page = valid[u] && blk < p.max_blocks ? bt[blk] : -1;
-            if (valid[u] && (page < 0 || page >= p.num_pages)) { bad = true; valid[u] = false; }
-            const __nv_bfloat16* pk = p.pool + (size_t)max(page, 0) * page_elems + ((size_t)kvh * p.page_size + (j - blk * p.page_size)) * kd;
-            const __nv_bfloat16* pv = p.pool + (size_t)max(page, 0) * page_elems + (size_t)p.nkv * p.page_size * kd +
-                                      ((size_t)kvh * p.page_size + (j - blk * p.page_size)) * Dv;
-            kraw[u] = make_uint4(0u, 0u, 0u, 0u);
-            vraw[u] = make_uint4(0u, 0u, 0u, 0u);
-            if (valid[u] && k_on) kraw[u] = *reinterpret_cast<const uint4*>(pk + li * 8);
-            if (valid[u] && v_on) vraw[u] = *reinterpret_cast<const uint4*>(pv + li * 8);
-        }
-#pragma unroll
-        for (int u = 0; u < U; ++u) {
-            if (round0 + u >= rounds) break;               // the same for every thread of the block
-            float kf[8], vf[8];
-            {
-                const __nv_bfloat162* k2 = reinterpret_cast<const __nv_bfloat162*>(&kraw[u]);
-                const __nv_bfloat162* v2 = reinterpret_cast<const __nv_bfloat162*>(&vraw[u]);
-#pragma unroll
-                for (int i = 0; i < 4; ++i) {
-                    const float2 a = __bfloat1622float2(k2[i]), b = __bfloat1622float2(v2[i]);
-                    kf[2 * i] = a.x; kf[2 * i + 1] = a.y; vf[2 * i] = b.x; vf[2 * i + 1] = b.y;
-                }
-            }
-#pragma unroll
-            for (int g = 0; g < G; ++g) {
-                float part = 0.0f;
-#pragma unroll
-                for (int i = 0; i < 8; ++i) part = fmaf(qf[g][i], kf[i], part);
-                float s[2] = {my_map == 0 ? part : 0.0f, my_map == 1 ? part : 0.0f};
-#pragma unroll
-                for (int o = GS / 2; o > 0; o >>= 1) {
-                    s[0] += __shfl_xor_sync(0xffffffffu, s[0], o);
-                    s[1] += __shfl_xor_sync(0xffffffffu, s[1], o);
-                }
-                if (valid[u])
-#pragma unroll
-                for (int m = 0; m < 2; ++m) {
-                    float sc = s[m] * p.scale;
-                    if (p.cap > 0.0f) sc = p.cap * tanh_exp(sc * inv_cap);
-                    const float mnew = fmaxf(mx[g][m], sc);
-                    const float corr = __expf(mx[g][m] - mnew), pr = __expf(sc - mnew);      // exp(-inf) = 0 on the first key
-                    sm[g][m] = sm[g][m] * corr + pr;
-#pragma unroll
-                    for (int i = 0; i < 8; ++i) acc[g][m][i] = fmaf(pr, vf[i], acc[g][m][i] * corr);
-                    mx[g][m] = mnew;
-                }
-            }
-        }
-    }
-    if (bad && li == 0) atomicOr(p.err, AIRUN_DEV_BAD_PAGE);
-    // ---- the groups of a warp into its first group
-#pragma unroll
-    for (int o = GS; o < 32; o <<= 1) {
-#pragma unroll
-        for (int g = 0; g < G; ++g)
-#pragma unroll
-            for (int m = 0; m < 2; ++m) {
-                const float m_o = __shfl_xor_sync(0xffffffffu, mx[g][m], o), s_o = __shfl_xor_sync(0xffffffffu, sm[g][m], o);
-                const float mnew = fmaxf(mx[g][m], m_o);
-                const float wa = mx[g][m] == -INFINITY ? 0.0f : __expf(mx[g][m] - mnew);
-                const float wb = m_o == -INFINITY ? 0.0f : __expf(m_o - mnew);
-                sm[g][m] = sm[g][m] * wa + s_o * wb;
-#pragma unroll
-                for (int i = 0; i < 8; ++i) {
-                    const float a_o = __shfl_xor_sync(0xffffffffu, acc[g][m][i], o);
-                    acc[g][m][i] = acc[g][m][i] * wa + a_o * wb;
-                }
-                mx[g][m] = mnew;
-            }
-    }
-    // ---- the warps through shared memory: [warp][g][m] -> maximum, sum, then 8*GS accumulator values
-    constexpr int ROW = 8 * GS + 2;
-    float* sh = reinterpret_cast<float*>(dam_smem);
-    if (lane < GS) {
-#pragma unroll
-        for (int g = 0; g < G; ++g)
-#pragma unroll
-            for (int m = 0; m < 2; ++m) {
-                float* row = sh + (size_t)((warp * G + g) * 2 + m) * ROW;
-                if (lane == 0) { row[0] = mx[g][m]; row[1] = sm[g][m]; }
-#pragma unroll
-                for (int i = 0; i < 8; ++i) row[2 + lane * 8 + i] = acc[g][m][i];
-            }
-    }
-    __syncthreads();
-    if (warp >= G) return;
-    const int g = warp, head = head0 + g;
-    float o[8];
-#pragma unroll
-    for (int i = 0; i < 8; ++i) o[i] = 0.0f;
-    const bool on = lane < GS && lane * 8 < Dv;
-#pragma unroll
-    for (int m = 0; m < 2; ++m) {
-        float gmax = -INFINITY, gsum = 0.0f, wgt[8];
-#pragma unroll
-        for (int w = 0; w < 8; ++w) gmax = fmaxf(gmax, sh[(size_t)((w * G + g) * 2 + m) * ROW]);
-#pragma unroll
-        for (int w = 0; w < 8; ++w) {
-            const float* row = sh + (size_t)((w * G + g) * 2 + m) * ROW;
-            wgt[w] = row[1] > 0.0f ? __expf(row[0] - gmax) : 0.0f;
-            gsum += row[1] * wgt[w];
-        }
-        const float inv = gsum > 0.0f ? 1.0f / gsum : 0.0f;
-        const float f = m == 0 ? inv : -p.lambda * inv;
-        if (on) {
-#pragma unroll
-            for (int i = 0; i < 8; ++i) {
-                float a = 0.0f;
-#pragma unroll
-                for (int w = 0; w < 8; ++w) a = fmaf(sh[(size_t)((w * G + g) * 2 + m) * ROW + 2 + lane * 8 + i], wgt[w], a);
-                o[i] = fmaf(a, f, o[i]);
-            }
-        }
-    }
-    float ss = 0.0f;
-#pragma unroll
-    for (int i = 0; i < 8; ++i) ss = fmaf(o[i], o[i], ss);
-    ss = warp_sum(ss);
-    const float nrm = p.out_scale / sqrtf(ss / (float)Dv + p.eps);
-    if (on) {
-        uint32_t w[4];
-#pragma unroll
-        for (int i = 0; i < 4; ++i) w[i] = pack_bf16(o[2 * i] * nrm, o[2 * i + 1] * nrm);
-        __nv_bfloat16* dst = p.out + (size_t)t * p.out_stride + (size_t)head * Dv + lane * 8;
-        if ((((size_t)dst) & 15) == 0) *reinterpret_cast<uint4*>(dst) = make_uint4(w[0], w[1], w[2], w[3]);
-        else {
-#pragma unroll
-            for (int i = 0; i < 4; ++i) *reinterpret_cast<uint32_t*>(dst + 2 * i) = w[i];
-        }
-    }
-}
-
-template <int G, int GS>
-static int dad_launch(const DamParams& p, cudaStream_t stream) {
-    const size_t smem = (size_t)8 * G * 2 * (8 * GS + 2) * sizeof(float);
-    static unsigned long long configured = 0;
-    if (smem > 48 * 1024 && first_on_device(configured)) {
-        cudaError_t e = cudaFuncSetAttribute(diff_attention_decode_kernel<G, GS>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
-        if (e != cudaSuccess) return (int)e;
-    }
-    airun_launch(diff_attention_decode_kernel<G, GS>, dim3(p.nkv * p.head_split, p.num_reqs), dim3(256), smem, stream, p);
-    return airun_launch_status();
-}
-
-// 1 when the decode kernel takes these sizes (the caller then lets the tile kernel skip single tokens).
-AIRUN_EXPORT int airun_diff_attention_decode_supported(int nh, int nkv, int D, int Dv) {
-    const int G = nkv > 0 && nh % nkv == 0 ? nh / nkv : 0;
-    return (G == 1 || G == 2 || G == 4 || G == 8) && D % 8 == 0 && Dv % 8 == 0 && 2 * D <= 256 && Dv <= 256;
-}
-
-// ---------------------------------------------------------------------------------------------------------
 // Single decoded tokens on the tensor cores.  One CTA (4 warps) per (request that brings ONE token, KV head): the
 // rows of the products are the G query heads of the group (up to 16), so every key and value row that is read
 // serves all of them and both maps.  The visible keys are walked in tiles of 64 through the same two asynchronous
@@ -579,10 +392,35 @@ __global__ __launch_bounds__(128) void diff_attention_group_kernel(const DamPara
     const float LOG2E = 1.4426950408889634f;
     const float cap_in = 2.0f * p.scale * inv_cap * LOG2E, cap2 = -2.0f * p.cap;
     bool bad = false;
+    // when the 16-byte pieces of a key's rows divide the CTA's threads evenly and pages are a power of two, each thread
+    // owns one piece (reg_*: where it lies in the page and in shared memory) for every key it copies
+    const int reg_lp = max(1, kd / 8 + Dv / 8);
+    const bool regular = vec && reg_lp <= 128 && 128 % reg_lp == 0 && (p.page_size & (p.page_size - 1)) == 0;
+    const int ps_shift = __ffs(p.page_size) - 1;
+    const int reg_u = tid % reg_lp, reg_key0 = tid / reg_lp, reg_step = 128 / reg_lp;
+    const bool reg_is_k = reg_u < kd / 8;
+    const int reg_c = reg_is_k ? reg_u * 8 : (reg_u - kd / 8) * 8;
+    const int reg_dst = reg_is_k ? (reg_c / D) * DP + reg_c % D : reg_c;
+    const int reg_stride = reg_is_k ? QS : VS, reg_row = reg_is_k ? kd : Dv;
+    const size_t reg_src = reg_is_k ? (size_t)kvh * p.page_size * kd + reg_c
+                                    : (size_t)p.nkv * p.page_size * kd + (size_t)kvh * p.page_size * Dv + reg_c;
     auto load_tile = [&](int kbase, int buf) {
         __nv_bfloat16* Ks = Ks0 + buf * DAM_KEYS * QS;
         __nv_bfloat16* Vs = Vs0 + buf * DAM_KEYS * VS;
         const int nk = min(DAM_KEYS, hi - kbase + 1);
+        if (regular) {
+            // a thread keeps its 16-byte column of the key (or value) row and walks the keys: nothing but the page
+            // lookup is worked out per copy
+            __nv_bfloat16* dst = (reg_is_k ? Ks : Vs) + reg_dst;
+            for (int key = reg_key0; key < nk; key += reg_step) {
+                const int j = kbase + key, blk = j >> ps_shift;
+                const int page = blk < p.max_blocks ? bt[blk] : -1;
+                if (page < 0 || page >= p.num_pages) { bad = true; continue; }
+                cp_async16(dst + key * reg_stride, p.pool + (size_t)page * page_elems + reg_src + (size_t)(j & (p.page_size - 1)) * reg_row);
+            }
+            cp_async_commit();
+            return;
+        }
         const int perk = vec ? kd / 8 : kd, perv = vec ? Dv / 8 : Dv;
         for (int e = tid; e < nk * (perk + perv); e += 128) {
             const int key = e / (perk + perv), u = e - key * (perk + perv);
@@ -815,41 +653,13 @@ AIRUN_EXPORT int airun_diff_attention_mma(const void* q, void* out, long long ou
     p.pool = (const __nv_bfloat16*)pool; p.block_table = block_table; p.max_blocks = max_blocks;
     p.cu_tokens = cu_tokens; p.context_lens = context_lens; p.num_reqs = num_reqs; p.num_pages = num_pages;
     p.page_size = page_size; p.nh = nh; p.nkv = nkv; p.D = D; p.Dv = Dv; p.scale = scale; p.cap = cap;
-    p.lambda = lambda; p.eps = eps; p.out_scale = out_scale; p.chunk = chunk; p.window = window; p.skip_single = skip_single; p.head_split = 1; p.err = err;
+    p.lambda = lambda; p.eps = eps; p.out_scale = out_scale; p.chunk = chunk; p.window = window; p.skip_single = skip_single; p.err = err;
     const int dp = D <= 32 ? 32 : D <= 64 ? 64 : 128, dvp = Dv <= 32 ? 32 : Dv <= 64 ? 64 : 128;
 #define DAM_CASE(A, B) if (dp == A && dvp == B) return dam_launch<A, B>(p, max_tiles, stream)
     DAM_CASE(32, 32); DAM_CASE(32, 64); DAM_CASE(32, 128);
     DAM_CASE(64, 32); DAM_CASE(64, 64); DAM_CASE(64, 128);
     DAM_CASE(128, 32); DAM_CASE(128, 64); DAM_CASE(128, 128);
 #undef DAM_CASE
-    return AIRUN_ERR_UNSUPPORTED;
-}
-
-// The single tokens of the batch (requests whose cu_tokens span is 1); every other request is skipped.
-AIRUN_EXPORT int airun_diff_attention_decode(const void* q, void* out, long long out_stride, const void* pool,
-                                             const int32_t* block_table, int max_blocks, const int32_t* cu_tokens,
-                                             const int32_t* context_lens, int num_reqs, int num_pages, int page_size,
-                                             int nh, int nkv, int D, int Dv, float scale, float cap, int chunk, int window,
-                                             float lambda, float eps, float out_scale, int* err, cudaStream_t stream) {
-    if (num_reqs < 0 || nh <= 0 || nkv <= 0 || page_size <= 0 || num_pages <= 0 || max_blocks <= 0 || chunk < 0 || window < 0 ||
-        !err || out_stride < (long long)nh * Dv || !cu_tokens || !context_lens || num_reqs > 65535 ||
-        !airun_diff_attention_decode_supported(nh, nkv, D, Dv) || (((uintptr_t)q | (uintptr_t)pool) & 15))
-        return AIRUN_ERR_ARG;
-    if (num_reqs == 0) return AIRUN_OK;
-    DamParams p;
-    p.q = (const __nv_bfloat16*)q; p.out = (__nv_bfloat16*)out; p.out_stride = out_stride;
-    p.pool = (const __nv_bfloat16*)pool; p.block_table = block_table; p.max_blocks = max_blocks;
-    p.cu_tokens = cu_tokens; p.context_lens = context_lens; p.num_reqs = num_reqs; p.num_pages = num_pages;
-    p.page_size = page_size; p.nh = nh; p.nkv = nkv; p.D = D; p.Dv = Dv; p.scale = scale; p.cap = cap;
-    p.lambda = lambda; p.eps = eps; p.out_scale = out_scale; p.chunk = chunk; p.window = window; p.skip_single = 0; p.err = err;
-    // groups of four or eight heads run as CTAs of two heads each (two such CTAs fit an SM at once; the keys they
-    // share come from the L2 cache for all but the first)
-    const int Gall = nh / nkv, G = Gall > 2 ? 2 : Gall;
-    p.head_split = Gall / G;
-    const int width = 2 * D > Dv ? 2 * D : Dv, gs = width <= 64 ? 8 : width <= 128 ? 16 : 32;
-#define DAD_CASE(A, B) if (G == A && gs == B) return dad_launch<A, B>(p, stream)
-    DAD_CASE(1, 8); DAD_CASE(1, 16); DAD_CASE(1, 32); DAD_CASE(2, 8); DAD_CASE(2, 16); DAD_CASE(2, 32);
-#undef DAD_CASE
     return AIRUN_ERR_UNSUPPORTED;
 }
 
@@ -870,7 +680,7 @@ AIRUN_EXPORT int airun_diff_attention_group(const void* q, void* out, long long 
     p.cu_tokens = cu_tokens; p.context_lens = context_lens; p.num_reqs = num_reqs; p.num_pages = num_pages;
     p.page_size = page_size; p.nh = nh; p.nkv = nkv; p.D = D; p.Dv = Dv; p.scale = scale; p.cap = cap;
     p.lambda = lambda; p.eps = eps; p.out_scale = out_scale; p.chunk = chunk; p.window = window; p.skip_single = 0;
-    p.head_split = 1; p.err = err;
+    p.err = err;
     const int dp = D <= 32 ? 32 : D <= 64 ? 64 : 128, dvp = Dv <= 32 ? 32 : Dv <= 64 ? 64 : 128;
 #define DAG_CASE(A, B) if (dp == A && dvp == B) return dag_launch<A, B>(p, stream)
     DAG_CASE(32, 32); DAG_CASE(32, 64); DAG_CASE(32, 128);

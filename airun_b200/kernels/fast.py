@@ -577,21 +577,12 @@ def diff_attention_bf16(ctx, q, out, cache, part) -> bool:
               int(part.window), float(part.lam), float(part.eps), 1.0 - float(part.lambda_init)]
     sig = [c_void_p, c_void_p, c_longlong, c_void_p, c_void_p, c_int, c_void_p, c_void_p, c_int]
     csig = [c_int, c_int, c_int, c_int, c_int, c_int, c_float, c_float, c_int, c_int, c_float, c_float, c_float]
-    # requests that bring ONE token go to a decode kernel, which finds them on the device (the tile kernel then skips
-    # them): the kernel in which lane groups take a key each (D and Dv multiples of 8, groups of 1, 2, 4 or 8 heads), or,
-    # for other sizes, the tensor-core kernel whose product rows are the query heads of a KV head (groups up to 16).
-    # The first is the faster one where both apply (190 against 326 us for 64 tokens over 1,024 keys at 16:8 heads of
-    # 2 x 64 / 128: the second spends its time on the address arithmetic of sixteen 16-byte copies a thread and tile).
-    lanes_ok = nh // nkv in (1, 2, 4, 8) and D % 8 == 0 and Dv % 8 == 0 and q.data_ptr() % 16 == 0 and pool.data_ptr() % 16 == 0
-    single = True
-    if "diff_decode" not in DISABLED and lanes_ok:
-        f = _fn("diff_attention_mma", "airun_diff_attention_decode", sig + csig + [c_void_p, c_void_p])
-        _check(f(*common, *consts, _p(ctx.err), _stream()), "diff_attention_decode")
-    elif "diff_group" not in DISABLED and nh // nkv <= 16:
+    # requests that bring ONE token go to the kernel whose product rows are the query heads of a KV head (groups of up
+    # to 16), which finds them on the device; the tile kernel then skips them
+    single = "diff_group" not in DISABLED and nh // nkv <= 16
+    if single:
         f = _fn("diff_attention_mma", "airun_diff_attention_group", sig + csig + [c_void_p, c_void_p])
         _check(f(*common, *consts, _p(ctx.err), _stream()), "diff_attention_group")
-    else:
-        single = False
     if single and getattr(ctx, "decode_only", False):
         return True
     # every other request's tokens are cut into tiles of 64; the kernel walks cu_tokens to find its tile, so the

@@ -378,13 +378,13 @@ def tensor_core_attention(case, lens, new, heads, kvh, D, Dv, scale, cap, lam, c
 @gpu
 @pytest.mark.parametrize("heads,kvh,D,Dv,chunk,page", [(6, 3, 16, 24, 37, 8), (2, 2, 8, 16, 11, 16), (4, 1, 40, 72, 0, 24),
                                                          (3, 1, 128, 128, 50, 16), (4, 2, 64, 128, 100, 16), (2, 1, 20, 36, 64, 16)])
-@pytest.mark.parametrize("single_tokens", ["lane groups", "head rows"])
+@pytest.mark.parametrize("single_tokens", ["head rows", "tiles"])
 def test_tensor_core_differential_attention_against_the_plain_formula(heads, kvh, D, Dv, chunk, page, single_tokens, monkeypatch):
-    """``single_tokens``: which kernel takes the requests that bring one token where both can (lane groups that take a key
-    each, or the tensor-core kernel whose product rows are the heads of a KV head)."""
+    """``single_tokens``: which kernel takes the requests that bring one token: the one whose product rows are the heads
+    of a KV head, or (that one switched off) the tile kernel like any portion."""
     from airun_b200.kernels import fast
-    if single_tokens == "head rows":
-        monkeypatch.setattr(fast, "DISABLED", set(fast.DISABLED) | {"diff_decode"})
+    if single_tokens == "tiles":
+        monkeypatch.setattr(fast, "DISABLED", set(fast.DISABLED) | {"diff_group"})
     lens, new = [150, 9, 77, 1, 64], [150, 1, 5, 1, 64]     # whole prompts (three and one tile), single tokens, a portion
     scale, cap, lam, eps, osc = D ** -0.5, 6.0, 0.45, 1e-5, 0.7
     case = paged_attention_case(lens, new, heads, kvh, D, Dv, chunk, page, torch.bfloat16, seed=heads + D)
