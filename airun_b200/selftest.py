@@ -303,6 +303,145 @@ def check_largest_logits(dev) -> Tuple[float, float]:
     return bad, 0.5
 
 
+def check_dyt_norm(dev) -> Tuple[float, float]:
+    from .kernels import ops
+    worst = 0.0
+    for T, H in ((5, 70), (300, 1024)):
+        x, d, v = torch.randn(T, H) * 2, torch.randn(T, H), torch.randn(H)
+        w, b, alpha = 1 + 0.3 * torch.randn(H), torch.randn(H), torch.tensor([0.6])
+        xd, out = x.to(dev), torch.empty(T, H, device=dev)
+        ops.dyt_norm(xd, alpha.to(dev), w.to(dev), b.to(dev), out, delta=d.to(dev), add_vec=v.to(dev))
+        sum_ = x.double() + d.double() + v.double()
+        worst = max(worst, _rel(out, torch.tanh(0.6 * sum_) * w.double() + b.double()), _rel(xd, sum_))
+    return worst, 1e-5
+
+
+def check_clamped_unit(dev) -> Tuple[float, float]:
+    """The clamped gated unit as a kernel of its own and as the epilogue of the tcgen05 gate/up product."""
+    from types import SimpleNamespace
+    from .kernels import fast, ops
+    T, H, inter, group, limit, slope = 70, 256, 160, 16, 1.5, 1.702
+    x = (torch.randn(T, H) * 0.5).to(torch.bfloat16)
+    wg, wu = (torch.randn(inter, H) * 0.2).to(torch.bfloat16), (torch.randn(inter, H) * 0.2).to(torch.bfloat16)
+    g = torch.clamp(x.double() @ wg.double().T, max=limit)
+    u = torch.clamp(x.double() @ wu.double().T, -limit, limit)
+    want = g * torch.sigmoid(slope * g) * (u + 1)
+    gu = torch.stack([(x.double() @ wg.double().T).view(T, -1, group), (x.double() @ wu.double().T).view(T, -1, group)], 2).reshape(T, 2 * inter)
+    out = torch.empty(T, inter, device=dev)
+    ops.glu_clamped(gu.float().to(dev), out, group, limit, slope)
+    worst = _rel(out, want)
+    w_gu = torch.stack([wg.view(-1, group, H), wu.view(-1, group, H)], 1).reshape(2 * inter, H).contiguous().to(dev)
+    buf = torch.zeros(T, inter + 8, device=dev, dtype=torch.bfloat16)
+    ctx = SimpleNamespace(err=torch.zeros(1, dtype=torch.int32, device=dev))
+    if not fast.linear_glu_clamped_bf16(ctx, x.to(dev), w_gu, buf[:, 8:], group, limit, slope):
+        raise RuntimeError("the fused gated unit refused sizes it should take")
+    return max(worst / 50, _rel(buf[:, 8:], want)), 1.5e-2          # bfloat16 output; the float32 kernel is held to 50x less
+
+
+def check_linear_attention(dev) -> Tuple[float, float]:
+    from .kernels import ops
+    heads, D, Dv, rank, tau, eps = 3, 40, 72, 6, 5.0, 1e-5
+    lens, kd, vd = [19, 1, 33], heads * D, heads * Dv
+    T = sum(lens)
+    proj = torch.randn(T, 2 * kd + 2 * vd + rank)
+    w2, b2, wn = torch.randn(kd, rank), torch.randn(kd) + 2, 1 + 0.2 * torch.randn(Dv)
+    pd = proj.to(dev)
+    cu = torch.tensor([0, 19, 20, 53], dtype=torch.int32, device=dev)
+    req = torch.repeat_interleave(torch.arange(3), torch.tensor(lens)).to(dev, torch.int32)
+    slots = torch.tensor([2, 0, 1], dtype=torch.int32, device=dev)
+    state = torch.zeros(3, heads, D, Dv, device=dev)
+    err = torch.zeros(1, dtype=torch.int32, device=dev)
+    decay, o, act = torch.empty(T, kd, device=dev), torch.empty(T, vd, device=dev), torch.empty(T, vd, device=dev)
+    ops.gla_decay(pd[:, 2 * kd + 2 * vd:], w2.to(dev), b2.to(dev), tau, decay, req)
+    ops.gla_recurrent(pd[:, :kd], pd[:, kd:2 * kd], pd[:, 2 * kd:2 * kd + vd], decay, state, cu, slots, 3, o, heads, D, Dv, D ** -0.5, err)
+    ops.gla_out_gate(o, pd[:, 2 * kd + vd:2 * kd + 2 * vd], wn.to(dev), eps, act, heads, Dv, req)
+    p64, worst, at = proj.double(), 0.0, 0
+    for n in lens:
+        rows = p64[at:at + n]
+        a = torch.exp(torch.nn.functional.logsigmoid(rows[:, 2 * kd + 2 * vd:] @ w2.double().T + b2.double()) / tau).view(n, heads, D)
+        q, k = rows[:, :kd].view(n, heads, D) * D ** -0.5, rows[:, kd:2 * kd].view(n, heads, D)
+        v, gate = rows[:, 2 * kd:2 * kd + vd].view(n, heads, Dv), rows[:, 2 * kd + vd:2 * kd + 2 * vd]
+        S, outs = torch.zeros(heads, D, Dv, dtype=torch.float64), []
+        for t in range(n):
+            S = a[t].unsqueeze(-1) * S + k[t].unsqueeze(-1) * v[t].unsqueeze(-2)
+            outs.append((S * q[t].unsqueeze(-1)).sum(1))
+        oo = torch.stack(outs)
+        oo = oo / torch.sqrt((oo * oo).mean(-1, keepdim=True) + eps) * wn.double()
+        worst = max(worst, _rel(act[at:at + n], oo.reshape(n, vd) * (gate * torch.sigmoid(gate))))
+        at += n
+    if int(err.item()):
+        raise RuntimeError("the recurrence reported a device error")
+    return worst, 2e-4
+
+
+def check_diff_attention(dev) -> Tuple[float, float]:
+    """Differential attention over scrambled pages: the float32 kernel, then the tensor-core kernels in bfloat16
+    (a whole prompt in tiles, a portion, single tokens)."""
+    from types import SimpleNamespace
+    from .kernels import fast, ops
+    heads, kvh, D, Dv, page, chunk = 4, 2, 16, 40, 8, 29
+    scale, cap, lam, eps, osc = D ** -0.5, 8.0, 0.4, 1e-5, 0.6
+    lens, new = [90, 12, 41], [90, 1, 7]
+    qw, kd = heads * 2 * D, 2 * D
+    worst = []
+    for dtype in (torch.float32, torch.bfloat16):
+        g = torch.Generator().manual_seed(4)
+        projs = [torch.randn(n, qw + kvh * (kd + Dv), generator=g) for n in lens]
+        if dtype == torch.bfloat16:
+            projs = [t.to(dtype).float() for t in projs]
+        nb = [(n + page - 1) // page for n in lens]
+        perm = torch.randperm(sum(nb) + 2, generator=g).tolist()
+        bt = torch.full((3, max(nb)), -1, dtype=torch.int32)
+        for r, n in enumerate(nb):
+            for b in range(n):
+                bt[r, b] = perm.pop()
+        pool = torch.zeros(sum(nb) + 2, page * kvh * (kd + Dv), device=dev, dtype=dtype)
+        err, btd = torch.zeros(1, dtype=torch.int32, device=dev), bt.to(dev)
+        for phase in (0, 1):
+            spans = [(0, n - m) if phase == 0 else (n - m, n) for n, m in zip(lens, new)]
+            rows = [r for r, (a, b) in enumerate(spans) if b > a]
+            if not rows:
+                continue
+            proj = torch.cat([projs[r][spans[r][0]:spans[r][1]] for r in rows]).to(dev)
+            pos = torch.cat([torch.arange(*spans[r]) for r in rows]).to(dev, torch.int32)
+            req = torch.cat([torch.full((spans[r][1] - spans[r][0],), r) for r in rows]).to(dev, torch.int32)
+            q = torch.empty(proj.shape[0], qw, device=dev, dtype=dtype)
+            ops.qkv_bias_store(proj, None, None, None, q, pool, btd, pos, req, 3, page, qw, kvh, kd, Dv, err)
+        out = torch.empty(q.shape[0], heads * Dv, device=dev, dtype=dtype)
+        if dtype == torch.float32:
+            ops.diff_attention(q, out, pool, btd, pos, req, 3, page, heads, kvh, D, Dv, scale, cap, chunk, 0, lam, eps, osc, err)
+        else:
+            counts = [spans[r][1] - spans[r][0] for r in range(3)]
+            ctx = SimpleNamespace(cu_tokens=torch.tensor([0, counts[0], counts[0] + counts[1], sum(counts)], dtype=torch.int32, device=dev),
+                                  context_lens=torch.tensor(lens, dtype=torch.int32, device=dev), num_reqs=3, err=err)
+            part = SimpleNamespace(D=D, Dv=Dv, nh=heads, nkv=kvh, scale=scale, cap=cap, chunk=chunk, window=0, lam=lam, eps=eps,
+                                   lambda_init=1.0 - osc)
+            if not fast.diff_attention_bf16(ctx, q, out, SimpleNamespace(pool=pool, block_table=btd, page_size=page), part):
+                raise RuntimeError("the tensor-core attention refused sizes it should take")
+        if int(err.item()):
+            raise RuntimeError("the attention reported a device error")
+        at, w = 0, 0.0
+        for r, n in enumerate(lens):
+            p64 = projs[r].double()
+            qq, kk = p64[:, :qw].view(n, heads, 2, D), p64[:, qw:qw + kvh * kd].view(n, kvh, 2, D)
+            vv = p64[:, qw + kvh * kd:].view(n, kvh, Dv)
+            i = torch.arange(n)
+            vis = (i[None, :] <= i[:, None]) & (i[None, :] // chunk == i[:, None] // chunk)
+            ref = torch.zeros(n, heads, Dv, dtype=torch.float64)
+            for h in range(heads):
+                maps = []
+                for m in range(2):
+                    sc = cap * torch.tanh((qq[:, h, m] @ kk[:, h // (heads // kvh), m].T) * scale / cap)
+                    maps.append(torch.softmax(sc.masked_fill(~vis, -math.inf), -1) @ vv[:, h // (heads // kvh)])
+                o = maps[0] - lam * maps[1]
+                ref[:, h] = o / torch.sqrt((o * o).mean(-1, keepdim=True) + eps) * osc
+            k = new[r]
+            w = max(w, _rel(out[at:at + k], ref.reshape(n, -1)[n - k:]))
+            at += k
+        worst.append(w)
+    return max(worst[0], worst[1] / 200), 1e-4                     # bfloat16 storage is held to 2e-2
+
+
 CHECKS: List[Tuple[str, Callable]] = [
     ("embedding gather", check_embedding),
     ("rmsnorm + residual add", check_rmsnorm),
@@ -315,6 +454,10 @@ CHECKS: List[Tuple[str, Callable]] = [
     ("attention, float32 generic", check_attention_generic),
     ("attention, tcgen05 prefill + split-K decode", check_attention_tensor_core),
     ("attention, mma.sync prefill + decode", check_attention_mma),
+    ("dynamic tanh norm + residual add", check_dyt_norm),
+    ("clamped gated unit, kernel and tcgen05 epilogue", check_clamped_unit),
+    ("gated linear attention: decay, recurrence, norm and gate", check_linear_attention),
+    ("differential attention, float32 and mma.sync", check_diff_attention),
     ("sampling", check_sampling),
     ("largest logits of a row", check_largest_logits),
 ]
