@@ -198,6 +198,10 @@ class VedizenConfig(ModelConfig):
             return None
         return "loop.step", self.loop_times
 
+    def ignorable_tensors(self) -> List[str]:
+        """Tensors a model file may hold although nothing reads them: the pass table of a loop that runs no layer."""
+        return [] if self.order_table() else ["loop.step"]
+
     def summary(self) -> str:
         kinds = "".join("g" if l["type"] == "gla" else "a" for l in self.layers)
         loop = (f", layers {self.loop_start}..{self.loop_stop - 1} x {self.loop_times}"

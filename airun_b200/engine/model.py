@@ -92,8 +92,9 @@ class DecoderModel:
         return specs
 
     def ignorable_tensors(self) -> List[str]:
-        # a tied model's file may still carry the head; it is the same matrix
-        return [self.names["head"]] if self.tied else []
+        # a tied model's file may still carry the head (it is the same matrix); a configuration may name more
+        extra = list(getattr(self.config, "ignorable_tensors", lambda: [])())
+        return ([self.names["head"]] if self.tied else []) + extra
 
     def load(self, source: TensorSource) -> None:
         tensors = load_tensors(self.weight_specs(), source, self.dtype, self.device, self.ignorable_tensors())

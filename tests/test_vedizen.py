@@ -526,6 +526,36 @@ def test_unequal_batches_with_slots_and_pages_used_again(folders, name, dtype):
             assert np.abs(one - got[i]).max() <= 2e-4 * np.abs(one).max()
 
 
+# ----------------------------------------------------------------------------- other orders of layers
+def order_cases():
+    g = lambda ff=None: P.gla_layer(2, 8, 24, tau=4.0, ff=ff)
+    a = lambda ff=None: P.attention_layer(3, 1, 8, 12, chunk=13, softcap=9.0, diff=0.4, ff=ff)
+    return {
+        "only linear attention, everything looped": P.make_config(96, 48, [g(40), g()], loop=(0, 2, 3), scale=0.7),
+        "only attention, no feed-forward anywhere": P.make_config(96, 48, [a(), a()], scale=1.3),
+        "loop at the end, once": P.make_config(96, 50, [a(32), g(32), a()], loop=(1, 3, 1)),
+        "a loop that runs no layer": P.make_config(96, 48, [g(24), a(24)], loop=(1, 1, 4)),
+        "one layer run five times": P.make_config(64, 40, [g(16)], loop=(0, 1, 5), eps=1e-3),
+    }
+
+
+@gpu
+@pytest.mark.parametrize("name", list(order_cases()))
+def test_other_orders_of_layers(name, tmp_path):
+    cfg = order_cases()[name]
+    W = P.random_weights(cfg, seed=3, rank=4)
+    stored = dict(W)
+    if "loop.step" not in stored and cfg.get("loop"):
+        stored["loop.step"] = torch.ones(cfg["loop"]["times"], cfg["width"], dtype=torch.bfloat16)     # a file may still hold it
+    folder = P.write_folder(str(tmp_path / "m"), cfg, stored)
+    seqs = [random_tokens(n, cfg["vocab"], 7 + n) for n in (45, 8)]
+    for dtype in ("float32", "bfloat16"):
+        eng = engine(folder, dtype, 8, tokens=192, batch=64)
+        got = run_schedule(eng, seqs, [[(0, 30), (1, 2)], [(0, 1), (1, 5)], [(0, 13), (1, 1)], [(0, 1)]])
+        for i, sq in enumerate(seqs):
+            compare(got[i], cfg, W, sq, dtype, f"{name}, request {i}")
+
+
 @gpu
 def test_long_decoding_across_many_chunks(folders):
     folder, cfg, W, page = folders["s1"]
