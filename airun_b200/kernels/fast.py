@@ -569,6 +569,7 @@ def diff_attention_bf16(ctx, q, out, cache, part) -> bool:
           "out must be row-major bfloat16 [T, heads*Dv]")
     pool, bt = cache.pool, cache.block_table
     _need(pool.is_contiguous() and pool[0].numel() == nkv * cache.page_size * (2 * D + Dv), "the cache pages do not fit the head sizes")
+    _need(q.data_ptr() % 16 == 0 and pool.data_ptr() % 16 == 0, "q and the cache pages must begin on 16-byte boundaries")
     _need(ctx.cu_tokens.numel() >= ctx.num_reqs + 1 and ctx.context_lens.numel() >= ctx.num_reqs,
           "the batch's layout arrays are shorter than its number of requests")
     common = [_p(q), _p(out), out.stride(0) if T > 1 else max(out.shape[1], out.stride(0)), _p(pool), _p(bt), bt.stride(0),
