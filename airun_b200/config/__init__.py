@@ -3,12 +3,14 @@ from .base import (ConfigError, LayerCall, LayerSpec, ModelConfig, architecture_
                    lookup_architecture, read_config_json, register_architecture, registered_architectures)
 from .qwen3 import Qwen3Config
 from .vedizen import VedizenConfig
+from .pogarax import PogaraxConfig
 
 
 def _register_builtin() -> None:
     from ..engine.model import build_decoder
     register_architecture("Qwen3ForCausalLM", Qwen3Config, build_decoder)
     register_architecture("Vedizen", VedizenConfig, build_decoder)
+    register_architecture("Pogarax", PogaraxConfig, build_decoder)
 
 
 _register_builtin()

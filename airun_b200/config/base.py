@@ -11,7 +11,7 @@ from __future__ import annotations
 
 import json
 import os
-from dataclasses import dataclass
+from dataclasses import dataclass, field
 from typing import Any, Callable, Dict, List, Optional, Tuple
 
 
@@ -34,6 +34,7 @@ class LayerSpec:
     norm: str
     norm_args: Dict[str, Any]
     arrangement: str = "pre_norm"
+    arrangement_args: Dict[str, Any] = field(default_factory=dict)      # constants of the arrangement itself
 
 
 @dataclass(frozen=True)

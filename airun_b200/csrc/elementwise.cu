@@ -510,3 +510,75 @@ AIRUN_EXPORT int airun_glu_clamped(const void* in, int in_dtype, void* out, int 
         return AIRUN_ERR_UNSUPPORTED;
     return airun_launch_status();
 }
+
+// Norm on a sub-layer's OUTPUT: x[t] += mult * y[t] / sqrt(mean(y[t]^2) + eps) * w, and, when `cast` is given,
+// cast[t] = x[t] in the compute type (the input of the sub-layer that follows, which reads x itself).  One block
+// per row; the row of y stays in registers between the two passes while it is short enough.
+template <typename TCast>
+__global__ __launch_bounds__(256) void postnorm_add_kernel(float* __restrict__ x, const float* __restrict__ y,
+                                                           const float* __restrict__ w, TCast* __restrict__ cast,
+                                                           int n, float eps, float mult) {
+    pdl_trigger();
+    pdl_wait();
+    __shared__ float red[33];
+    const int r = blockIdx.x;
+    float* xr = x + (size_t)r * n;
+    const float* yr = y + (size_t)r * n;
+    float keep[8];
+    float ss = 0.0f;
+#pragma unroll
+    for (int k = 0; k < 8; ++k) {
+        const int i = threadIdx.x + k * 256;
+        keep[k] = i < n ? yr[i] : 0.0f;
+        ss = fmaf(keep[k], keep[k], ss);
+    }
+    for (int i = threadIdx.x + 8 * 256; i < n; i += 256) ss = fmaf(yr[i], yr[i], ss);
+    ss = block_sum(ss, red);
+    const float inv = 1.0f / sqrtf(ss / (float)n + eps);
+#pragma unroll
+    for (int k = 0; k < 8; ++k) {
+        const int i = threadIdx.x + k * 256;
+        if (i < n) {
+            const float v = xr[i] + mult * (keep[k] * inv * w[i]);
+            xr[i] = v;
+            if (cast) cast[(size_t)r * n + i] = from_f32<TCast>(v);
+        }
+    }
+    for (int i = threadIdx.x + 8 * 256; i < n; i += 256) {
+        const float v = xr[i] + mult * (yr[i] * inv * w[i]);
+        xr[i] = v;
+        if (cast) cast[(size_t)r * n + i] = from_f32<TCast>(v);
+    }
+}
+
+AIRUN_EXPORT int airun_postnorm_add(float* x, const float* y, const float* w, void* cast, int cast_dtype, int T, int n,
+                                    float eps, float mult, cudaStream_t stream) {
+    if (T < 0 || n <= 0 || !x || !y || !w) return AIRUN_ERR_ARG;
+    if (T == 0) return AIRUN_OK;
+    if (!cast || cast_dtype == AIRUN_DT_F32)
+        airun_launch(postnorm_add_kernel<float>, dim3(T), dim3(256), 0, stream, x, y, w, (float*)cast, n, eps, mult);
+    else if (cast_dtype == AIRUN_DT_BF16)
+        airun_launch(postnorm_add_kernel<__nv_bfloat16>, dim3(T), dim3(256), 0, stream, x, y, w, (__nv_bfloat16*)cast, n, eps, mult);
+    else
+        return AIRUN_ERR_UNSUPPORTED;
+    return airun_launch_status();
+}
+
+// out = in in another type (float32 -> bfloat16 or a plain copy), n elements.
+template <typename TOut>
+__global__ void cast_kernel(const float* __restrict__ in, TOut* __restrict__ out, long long n) {
+    pdl_trigger();
+    pdl_wait();
+    for (long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x; i < n; i += (long long)gridDim.x * blockDim.x)
+        out[i] = from_f32<TOut>(in[i]);
+}
+
+AIRUN_EXPORT int airun_cast_f32(const float* in, void* out, int out_dtype, long long n, cudaStream_t stream) {
+    if (n < 0 || !in || !out) return AIRUN_ERR_ARG;
+    if (n == 0) return AIRUN_OK;
+    const int blocks = (int)((n + 1023) / 1024 > 148 * 8 ? 148 * 8 : (n + 1023) / 1024);
+    if (out_dtype == AIRUN_DT_F32) airun_launch(cast_kernel<float>, dim3(blocks), dim3(256), 0, stream, in, (float*)out, n);
+    else if (out_dtype == AIRUN_DT_BF16) airun_launch(cast_kernel<__nv_bfloat16>, dim3(blocks), dim3(256), 0, stream, in, (__nv_bfloat16*)out, n);
+    else return AIRUN_ERR_UNSUPPORTED;
+    return airun_launch_status();
+}

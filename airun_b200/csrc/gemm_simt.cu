@@ -14,17 +14,45 @@
 #define TK 16
 #define PAD 4
 
-template <typename TA, typename TW, typename TC>
+// Two more forms of the same tile loop.  BATCHED: blockIdx.z names one of several products of equal sizes whose
+// operands lie `sa`, `sw`, `sc` elements apart (the heads of a per-head product over column slices of one buffer).
+// GROUPED: the rows of A are cut into segments, segment e = rows seg[e] .. seg[e + 1] - 1 (device memory), and the
+// rows of segment e are multiplied by the matrix W + e * sw; blockIdx.y counts the row tiles of all segments in
+// turn, and a block beyond the last tile leaves at once, so one launch of a fixed shape serves any cut.
+struct GemmExtra {
+    long long sa, sw, sc;          // strides between the products of a batch; sw also between the matrices of segments
+    const int32_t* seg;            // [n_seg + 1] row offsets of the segments (GROUPED)
+    int n_seg;
+};
+
+template <typename TA, typename TW, typename TC, int FORM>      // FORM 0 plain, 1 batched, 2 grouped
 __global__ __launch_bounds__(256) void gemm_simt_kernel(
     const TA* __restrict__ A, const TW* __restrict__ W, TC* __restrict__ C,
-    int M, int N, int K, long long lda, long long ldw, long long ldc) {
+    int M, int N, int K, long long lda, long long ldw, long long ldc, GemmExtra ex) {
     pdl_trigger();
     pdl_wait();
     __shared__ __align__(16) float As[TK][TM + PAD];
     __shared__ __align__(16) float Ws[TK][TN + PAD];
     const int tid = threadIdx.x;
     const int tx = tid & 15, ty = tid >> 4;
-    const int m0 = blockIdx.y * TM, n0 = blockIdx.x * TN;
+    int m0 = blockIdx.y * TM;
+    const int n0 = blockIdx.x * TN;
+    if (FORM == 1) {
+        A += (size_t)blockIdx.z * ex.sa;
+        W += (size_t)blockIdx.z * ex.sw;
+        C += (size_t)blockIdx.z * ex.sc;
+    }
+    if (FORM == 2) {
+        int tile = blockIdx.y, e = 0, found = 0;
+        for (; e < ex.n_seg; ++e) {
+            const int lo = ex.seg[e], hi = ex.seg[e + 1];
+            const int tiles = (hi - lo + TM - 1) / TM;
+            if (tile < tiles) { m0 = lo + tile * TM; M = min(M, hi); found = 1; break; }
+            tile -= tiles;
+        }
+        if (!found) return;
+        W += (size_t)e * ex.sw;
+    }
     const int lr = tid >> 2, lk = (tid & 3) * 4;
 
     float acc[4][4];
@@ -79,8 +107,50 @@ AIRUN_EXPORT int airun_gemm_simt(const void* A, int a_dtype, const void* W, int 
     if (M == 0) return AIRUN_OK;
     dim3 grid(ceil_div_i(N, TN), ceil_div_i(M, TM));
     if (grid.y > 65535) return AIRUN_ERR_ARG;
+    GemmExtra ex = {};
 #define LAUNCH(TA, TW, TC) \
-    airun_launch(gemm_simt_kernel<TA, TW, TC>, dim3(grid), dim3(256), 0, stream, (const TA*)A, (const TW*)W, (TC*)C, M, N, K, lda, ldw, ldc)
+    airun_launch(gemm_simt_kernel<TA, TW, TC, 0>, dim3(grid), dim3(256), 0, stream, (const TA*)A, (const TW*)W, (TC*)C, M, N, K, lda, ldw, ldc, ex)
+    if (a_dtype == AIRUN_DT_F32 && w_dtype == AIRUN_DT_F32 && c_dtype == AIRUN_DT_F32) LAUNCH(float, float, float);
+    else if (a_dtype == AIRUN_DT_BF16 && w_dtype == AIRUN_DT_BF16 && c_dtype == AIRUN_DT_F32) LAUNCH(__nv_bfloat16, __nv_bfloat16, float);
+    else if (a_dtype == AIRUN_DT_BF16 && w_dtype == AIRUN_DT_BF16 && c_dtype == AIRUN_DT_BF16) LAUNCH(__nv_bfloat16, __nv_bfloat16, __nv_bfloat16);
+    else return AIRUN_ERR_UNSUPPORTED;
+#undef LAUNCH
+    return airun_launch_status();
+}
+
+// `batch` products of equal sizes, product b on A + b*sa, W + b*sw, C + b*sc (elements).
+AIRUN_EXPORT int airun_gemm_simt_batched(const void* A, int a_dtype, const void* W, int w_dtype, void* C, int c_dtype,
+                                         int M, int N, int K, long long lda, long long ldw, long long ldc, int batch,
+                                         long long sa, long long sw, long long sc, cudaStream_t stream) {
+    if (M < 0 || N <= 0 || K <= 0 || lda < K || ldw < K || ldc < N || batch <= 0 || batch > 65535) return AIRUN_ERR_ARG;
+    if (M == 0) return AIRUN_OK;
+    dim3 grid(ceil_div_i(N, TN), ceil_div_i(M, TM), batch);
+    if (grid.y > 65535) return AIRUN_ERR_ARG;
+    GemmExtra ex = {};
+    ex.sa = sa; ex.sw = sw; ex.sc = sc;
+#define LAUNCH(TA, TW, TC) \
+    airun_launch(gemm_simt_kernel<TA, TW, TC, 1>, dim3(grid), dim3(256), 0, stream, (const TA*)A, (const TW*)W, (TC*)C, M, N, K, lda, ldw, ldc, ex)
+    if (a_dtype == AIRUN_DT_F32 && w_dtype == AIRUN_DT_F32 && c_dtype == AIRUN_DT_F32) LAUNCH(float, float, float);
+    else if (a_dtype == AIRUN_DT_BF16 && w_dtype == AIRUN_DT_BF16 && c_dtype == AIRUN_DT_F32) LAUNCH(__nv_bfloat16, __nv_bfloat16, float);
+    else if (a_dtype == AIRUN_DT_BF16 && w_dtype == AIRUN_DT_BF16 && c_dtype == AIRUN_DT_BF16) LAUNCH(__nv_bfloat16, __nv_bfloat16, __nv_bfloat16);
+    else return AIRUN_ERR_UNSUPPORTED;
+#undef LAUNCH
+    return airun_launch_status();
+}
+
+// The rows of A in `n_seg` segments (`seg`: int32 [n_seg + 1] on the device, rising, seg[n_seg] <= M); rows of
+// segment e times W + e*sw.  The launch covers ceil(M / TM) + n_seg row tiles, which is enough for every cut.
+AIRUN_EXPORT int airun_gemm_simt_grouped(const void* A, int a_dtype, const void* W, int w_dtype, void* C, int c_dtype,
+                                         int M, int N, int K, long long lda, long long ldw, long long ldc,
+                                         const int32_t* seg, int n_seg, long long sw, cudaStream_t stream) {
+    if (M < 0 || N <= 0 || K <= 0 || lda < K || ldw < K || ldc < N || !seg || n_seg <= 0) return AIRUN_ERR_ARG;
+    if (M == 0) return AIRUN_OK;
+    dim3 grid(ceil_div_i(N, TN), ceil_div_i(M, TM) + n_seg);
+    if (grid.y > 65535) return AIRUN_ERR_ARG;
+    GemmExtra ex = {};
+    ex.sw = sw; ex.seg = seg; ex.n_seg = n_seg;
+#define LAUNCH(TA, TW, TC) \
+    airun_launch(gemm_simt_kernel<TA, TW, TC, 2>, dim3(grid), dim3(256), 0, stream, (const TA*)A, (const TW*)W, (TC*)C, M, N, K, lda, ldw, ldc, ex)
     if (a_dtype == AIRUN_DT_F32 && w_dtype == AIRUN_DT_F32 && c_dtype == AIRUN_DT_F32) LAUNCH(float, float, float);
     else if (a_dtype == AIRUN_DT_BF16 && w_dtype == AIRUN_DT_BF16 && c_dtype == AIRUN_DT_F32) LAUNCH(__nv_bfloat16, __nv_bfloat16, float);
     else if (a_dtype == AIRUN_DT_BF16 && w_dtype == AIRUN_DT_BF16 && c_dtype == AIRUN_DT_BF16) LAUNCH(__nv_bfloat16, __nv_bfloat16, __nv_bfloat16);

@@ -16,18 +16,30 @@
 #include "common.cuh"
 
 // a[t][c] = exp(logsigmoid(bias[c] + sum_j low[t][j] * w2[c][j]) / tau) for c < n (= heads * D).
+// The same kernel serves every second half of a low-rank pair that ends in a function of its own, in float32:
+// with z = bias[c] + sum_j f(low[t][j]) * w2[c][j] (f the identity, or tanh when `in_tanh`),
+//   LOWRANK_POW_SIGMOID   sigmoid(z)^(1/tau)
+//   LOWRANK_EXP_SOFTPLUS  exp(-exp(p[c / group]) * softplus(z))     (p: one number per group of channels)
+//   LOWRANK_SIGMOID       sigmoid(z)
+//   LOWRANK_EXP_NEG_EXP   exp(-exp(z))
+#define LOWRANK_POW_SIGMOID 0
+#define LOWRANK_EXP_SOFTPLUS 1
+#define LOWRANK_SIGMOID 2
+#define LOWRANK_EXP_NEG_EXP 3
 #define DECAY_TOKENS 8        // tokens of one block: a row of w2 is read once for all of them
 template <typename TW>
 __global__ __launch_bounds__(128) void decay_kernel(const float* __restrict__ low, long long low_stride, const TW* __restrict__ w2,
                                                     const float* __restrict__ bias, float* __restrict__ out, int T, int n, int rank,
-                                                    float inv_tau, const int32_t* __restrict__ req_of_token) {
+                                                    float inv_tau, const int32_t* __restrict__ req_of_token,
+                                                    int mode, int in_tanh, const float* __restrict__ group_param, int group) {
     pdl_trigger();
     pdl_wait();
     extern __shared__ float s_low[];                       // [DECAY_TOKENS][rank]
     const int t0 = blockIdx.x * DECAY_TOKENS, nt = min(DECAY_TOKENS, T - t0);
     for (int e = threadIdx.x; e < nt * rank; e += blockDim.x) {
         const int tk = e / rank, j = e - tk * rank;
-        s_low[e] = low[(size_t)(t0 + tk) * low_stride + j];
+        const float lv = low[(size_t)(t0 + tk) * low_stride + j];
+        s_low[e] = in_tanh ? tanhf(lv) : lv;
     }
     __syncthreads();
     const int c = blockIdx.y * blockDim.x + threadIdx.x;       // a channel a thread
@@ -46,27 +58,40 @@ __global__ __launch_bounds__(128) void decay_kernel(const float* __restrict__ lo
 #pragma unroll
         for (int tk = 0; tk < DECAY_TOKENS; ++tk) {
             if (tk >= nt || req_of_token[t0 + tk] < 0) continue;
-            // logsigmoid(z) = min(z, 0) - log(1 + exp(-|z|))
-            const float ls = fminf(z[tk], 0.0f) - log1pf(expf(-fabsf(z[tk])));
-            out[(size_t)(t0 + tk) * n + c] = expf(ls * inv_tau);
+            const float zz = z[tk], l1p = log1pf(expf(-fabsf(zz)));
+            float r;
+            if (mode == LOWRANK_POW_SIGMOID) r = expf((fminf(zz, 0.0f) - l1p) * inv_tau);      // logsigmoid(z) = min(z, 0) - log(1 + exp(-|z|))
+            else if (mode == LOWRANK_EXP_SOFTPLUS) r = expf(-expf(group_param[c / group]) * (fmaxf(zz, 0.0f) + l1p));
+            else if (mode == LOWRANK_SIGMOID) r = 1.0f / (1.0f + expf(-zz));
+            else r = expf(-expf(zz));
+            out[(size_t)(t0 + tk) * n + c] = r;
         }
     }
 }
 
-AIRUN_EXPORT int airun_gla_decay(const float* low, long long low_stride, const void* w2, int w_dtype, const float* bias,
-                                     float* out, int T, int n, int rank, float tau, const int32_t* req_of_token,
-                                     cudaStream_t stream) {
-    if (T < 0 || n <= 0 || n > 65535 * 128 || rank <= 0 || rank > 1024 || !(tau > 0.0f) || !req_of_token) return AIRUN_ERR_ARG;
+AIRUN_EXPORT int airun_lowrank_act(const float* low, long long low_stride, const void* w2, int w_dtype, const float* bias,
+                                   float* out, int T, int n, int rank, float tau, const int32_t* req_of_token,
+                                   int mode, int in_tanh, const float* group_param, int group, cudaStream_t stream) {
+    if (T < 0 || n <= 0 || n > 65535 * 128 || rank <= 0 || rank > 1024 || !(tau > 0.0f) || !req_of_token || mode < 0 || mode > 3)
+        return AIRUN_ERR_ARG;
+    if (mode == LOWRANK_EXP_SOFTPLUS && (!group_param || group <= 0)) return AIRUN_ERR_ARG;
     if (T == 0) return AIRUN_OK;
     const size_t smem = (size_t)DECAY_TOKENS * rank * sizeof(float);
     const int blocks = ceil_div_i(T, DECAY_TOKENS);
     if (w_dtype == AIRUN_DT_F32)
-        airun_launch(decay_kernel<float>, dim3(blocks, ceil_div_i(n, 128)), dim3(128), smem, stream, low, low_stride, (const float*)w2, bias, out, T, n, rank, 1.0f / tau, req_of_token);
+        airun_launch(decay_kernel<float>, dim3(blocks, ceil_div_i(n, 128)), dim3(128), smem, stream, low, low_stride, (const float*)w2, bias, out, T, n, rank, 1.0f / tau, req_of_token, mode, in_tanh, group_param, group);
     else if (w_dtype == AIRUN_DT_BF16)
-        airun_launch(decay_kernel<__nv_bfloat16>, dim3(blocks, ceil_div_i(n, 128)), dim3(128), smem, stream, low, low_stride, (const __nv_bfloat16*)w2, bias, out, T, n, rank, 1.0f / tau, req_of_token);
+        airun_launch(decay_kernel<__nv_bfloat16>, dim3(blocks, ceil_div_i(n, 128)), dim3(128), smem, stream, low, low_stride, (const __nv_bfloat16*)w2, bias, out, T, n, rank, 1.0f / tau, req_of_token, mode, in_tanh, group_param, group);
     else
         return AIRUN_ERR_UNSUPPORTED;
     return airun_launch_status();
+}
+
+AIRUN_EXPORT int airun_gla_decay(const float* low, long long low_stride, const void* w2, int w_dtype, const float* bias,
+                                 float* out, int T, int n, int rank, float tau, const int32_t* req_of_token,
+                                 cudaStream_t stream) {
+    return airun_lowrank_act(low, low_stride, w2, w_dtype, bias, out, T, n, rank, tau, req_of_token, LOWRANK_POW_SIGMOID, 0,
+                             nullptr, 0, stream);
 }
 
 // The recurrence.  One block per (request, head, 32 value columns), 256 threads: a lane owns a column
@@ -224,13 +249,17 @@ template <typename TOut>
 __global__ __launch_bounds__(128) void out_gate_kernel(const float* __restrict__ o, const float* __restrict__ gate,
                                                        long long gate_stride, const float* __restrict__ w,
                                                        TOut* __restrict__ out, long long out_stride, int T, int heads,
-                                                       int Dv, float eps, const int32_t* __restrict__ req_of_token) {
+                                                       int Dv, float eps, const int32_t* __restrict__ req_of_token,
+                                                       int gate_act, int w_per_head) {
     pdl_trigger();
     pdl_wait();
     const int unit = blockIdx.x * 4 + (threadIdx.x >> 5), lane = threadIdx.x & 31;
     if (unit >= T * heads) return;
     const int t = unit / heads, h = unit - t * heads;
     if (req_of_token[t] < 0) return;
+    if (w && w_per_head) w += (size_t)h * Dv;
+    // the gate: silu(g) (0), sigmoid(g) (1), or g as it is (2: the caller has applied its function already)
+    auto gf = [&](float g) { return gate_act == 0 ? g / (1.0f + expf(-g)) : gate_act == 1 ? 1.0f / (1.0f + expf(-g)) : g; };
     const float* orow = o + ((size_t)t * heads + h) * Dv;
     const float* grow = gate + (size_t)t * gate_stride + (size_t)h * Dv;
     TOut* dst = out + (size_t)t * out_stride + (size_t)h * Dv;
@@ -246,10 +275,10 @@ __global__ __launch_bounds__(128) void out_gate_kernel(const float* __restrict__
         const float ss4 = warp_sum(ov.x * ov.x + ov.y * ov.y + ov.z * ov.z + ov.w * ov.w);
         const float inv4 = 1.0f / sqrtf(ss4 / (float)Dv + eps);
         if (on) {
-            dst[lane * 4 + 0] = from_f32<TOut>(ov.x * inv4 * wv.x * (gv.x / (1.0f + expf(-gv.x))));
-            dst[lane * 4 + 1] = from_f32<TOut>(ov.y * inv4 * wv.y * (gv.y / (1.0f + expf(-gv.y))));
-            dst[lane * 4 + 2] = from_f32<TOut>(ov.z * inv4 * wv.z * (gv.z / (1.0f + expf(-gv.z))));
-            dst[lane * 4 + 3] = from_f32<TOut>(ov.w * inv4 * wv.w * (gv.w / (1.0f + expf(-gv.w))));
+            dst[lane * 4 + 0] = from_f32<TOut>(ov.x * inv4 * wv.x * gf(gv.x));
+            dst[lane * 4 + 1] = from_f32<TOut>(ov.y * inv4 * wv.y * gf(gv.y));
+            dst[lane * 4 + 2] = from_f32<TOut>(ov.z * inv4 * wv.z * gf(gv.z));
+            dst[lane * 4 + 3] = from_f32<TOut>(ov.w * inv4 * wv.w * gf(gv.w));
         }
         return;
     }
@@ -259,20 +288,20 @@ __global__ __launch_bounds__(128) void out_gate_kernel(const float* __restrict__
     const float inv = 1.0f / sqrtf(ss / (float)Dv + eps);
     for (int j = lane; j < Dv; j += 32) {
         const float g = grow[j];
-        dst[j] = from_f32<TOut>(orow[j] * inv * (w ? w[j] : 1.0f) * (g / (1.0f + expf(-g))));
+        dst[j] = from_f32<TOut>(orow[j] * inv * (w ? w[j] : 1.0f) * gf(g));
     }
 }
 
 AIRUN_EXPORT int airun_gla_out_gate(const float* o, const float* gate, long long gate_stride, const float* w, void* out,
                                     int out_dtype, long long out_stride, int T, int heads, int Dv, float eps,
-                                    const int32_t* req_of_token, cudaStream_t stream) {
+                                    const int32_t* req_of_token, int gate_act, int w_per_head, cudaStream_t stream) {
     if (T < 0 || heads <= 0 || Dv <= 0 || !req_of_token || out_stride < (long long)heads * Dv) return AIRUN_ERR_ARG;
     if (T == 0) return AIRUN_OK;
     const int blocks = ceil_div_i((long long)T * heads, 4);
     if (out_dtype == AIRUN_DT_F32)
-        airun_launch(out_gate_kernel<float>, dim3(blocks), dim3(128), 0, stream, o, gate, gate_stride, w, (float*)out, out_stride, T, heads, Dv, eps, req_of_token);
+        airun_launch(out_gate_kernel<float>, dim3(blocks), dim3(128), 0, stream, o, gate, gate_stride, w, (float*)out, out_stride, T, heads, Dv, eps, req_of_token, gate_act, w_per_head);
     else if (out_dtype == AIRUN_DT_BF16)
-        airun_launch(out_gate_kernel<__nv_bfloat16>, dim3(blocks), dim3(128), 0, stream, o, gate, gate_stride, w, (__nv_bfloat16*)out, out_stride, T, heads, Dv, eps, req_of_token);
+        airun_launch(out_gate_kernel<__nv_bfloat16>, dim3(blocks), dim3(128), 0, stream, o, gate, gate_stride, w, (__nv_bfloat16*)out, out_stride, T, heads, Dv, eps, req_of_token, gate_act, w_per_head);
     else
         return AIRUN_ERR_UNSUPPORTED;
     return airun_launch_status();

@@ -1,0 +1,171 @@
+// A routed feed-forward: every token goes to the `top` experts with the largest scores.
+//
+//   z = Wr h (float32),  s = sigmoid(z) or softmax(z);  the `top` largest s (equal scores: the lower id first)
+//   weight = s of the chosen expert, divided by the sum of the chosen ones when `renorm`
+// The rows of a step are then sorted by expert so that every expert's rows are one segment of a buffer and a
+// grouped product (gemm_simt.cu) runs each segment against its expert's matrices:
+//   route    ids, weights, and each row's rank among its expert's rows (a counter per expert)
+//   offsets  seg[e] = rows of the experts before e
+//   scatter  xs[seg[e] + rank] = h[t] (times the weight, when the weight scales the expert's INPUT)
+//   ...      the experts' products on xs ...
+//   combine  out[t] = sum over the token's experts, in the order they were chosen, of ys[row] (times the weight,
+//            when it scales the output)
+// A row's result depends on the row alone, so the order in which rows reach a segment (the counters are atomic)
+// does not show in the result.  Rows of request -1 are padding: they are routed nowhere.
+#include "common.cuh"
+
+#define MOE_MAX_EXPERTS 1024
+
+template <typename TH>
+__global__ __launch_bounds__(128) void moe_route_kernel(
+    const TH* __restrict__ h, const TH* __restrict__ wr, int W, int E, int top, int softmax_scores, int renorm,
+    const int32_t* __restrict__ req_of_token, int32_t* __restrict__ ids, float* __restrict__ wts, int32_t* __restrict__ rank,
+    int32_t* __restrict__ counts) {
+    pdl_trigger();
+    pdl_wait();
+    __shared__ float s_score[MOE_MAX_EXPERTS];
+    const int t = blockIdx.x;
+    if (req_of_token[t] < 0) {
+        for (int k = threadIdx.x; k < top; k += blockDim.x) ids[(size_t)t * top + k] = -1;
+        return;
+    }
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const TH* hr = h + (size_t)t * W;
+    for (int e = warp; e < E; e += 4) {
+        const TH* w = wr + (size_t)e * W;
+        float acc = 0.0f;
+        for (int c = lane; c < W; c += 32) acc = fmaf(to_f32<TH>(hr[c]), to_f32<TH>(w[c]), acc);
+        acc = warp_sum(acc);
+        if (lane == 0) s_score[e] = acc;
+    }
+    __syncthreads();
+    if (warp != 0) return;
+    if (softmax_scores) {
+        float m = -INFINITY;
+        for (int e = lane; e < E; e += 32) m = fmaxf(m, s_score[e]);
+        m = warp_max(m);
+        float sum = 0.0f;
+        for (int e = lane; e < E; e += 32) { const float p = expf(s_score[e] - m); s_score[e] = p; sum += p; }
+        sum = warp_sum(sum);
+        for (int e = lane; e < E; e += 32) s_score[e] /= sum;
+    } else {
+        for (int e = lane; e < E; e += 32) s_score[e] = 1.0f / (1.0f + expf(-s_score[e]));
+    }
+    __syncwarp();
+    float total = 0.0f;
+    for (int k = 0; k < top; ++k) {
+        float best = -INFINITY;
+        int arg = E;
+        for (int e = lane; e < E; e += 32) {
+            const float v = s_score[e];
+            if (v > best) { best = v; arg = e; }          // within a lane ids rise, so the first of equals stays
+        }
+#pragma unroll
+        for (int o = 16; o > 0; o >>= 1) {
+            const float ob = __shfl_xor_sync(0xffffffffu, best, o);
+            const int oa = __shfl_xor_sync(0xffffffffu, arg, o);
+            if (ob > best || (ob == best && oa < arg)) { best = ob; arg = oa; }
+        }
+        if (arg >= E) arg = 0;                              // a row of NaN scores: still a valid expert
+        total += best;
+        if (lane == 0) {
+            ids[(size_t)t * top + k] = arg;
+            wts[(size_t)t * top + k] = best;
+            rank[(size_t)t * top + k] = atomicAdd(&counts[arg], 1);
+            s_score[arg] = -INFINITY;
+        }
+        __syncwarp();
+    }
+    if (renorm && lane == 0)
+        for (int k = 0; k < top; ++k) wts[(size_t)t * top + k] /= total;
+}
+
+__global__ void moe_offsets_kernel(const int32_t* __restrict__ counts, int32_t* __restrict__ seg, int E) {
+    pdl_trigger();
+    pdl_wait();
+    if (threadIdx.x == 0 && blockIdx.x == 0) {
+        int at = 0;
+        seg[0] = 0;
+        for (int e = 0; e < E; ++e) { at += counts[e]; seg[e + 1] = at; }
+    }
+}
+
+template <typename TH>
+__global__ __launch_bounds__(256) void moe_scatter_kernel(
+    const TH* __restrict__ h, int W, int top, const int32_t* __restrict__ ids, const float* __restrict__ wts,
+    const int32_t* __restrict__ rank, const int32_t* __restrict__ seg, int scale_input, TH* __restrict__ xs,
+    int32_t* __restrict__ row_of) {
+    pdl_trigger();
+    pdl_wait();
+    const int t = blockIdx.x;
+    for (int k = 0; k < top; ++k) {
+        const int e = ids[(size_t)t * top + k];
+        if (e < 0) return;
+        const int row = seg[e] + rank[(size_t)t * top + k];
+        if (threadIdx.x == 0) row_of[(size_t)t * top + k] = row;
+        const float w = scale_input ? wts[(size_t)t * top + k] : 1.0f;
+        for (int c = threadIdx.x; c < W; c += blockDim.x)
+            xs[(size_t)row * W + c] = from_f32<TH>(w * to_f32<TH>(h[(size_t)t * W + c]));
+    }
+}
+
+__global__ __launch_bounds__(256) void moe_combine_kernel(
+    const float* __restrict__ ys, int W, int top, const int32_t* __restrict__ ids, const float* __restrict__ wts,
+    const int32_t* __restrict__ row_of, int scale_output, float* __restrict__ out) {
+    pdl_trigger();
+    pdl_wait();
+    const int t = blockIdx.x;
+    const bool pad = ids[(size_t)t * top] < 0;
+    for (int c = threadIdx.x; c < W; c += blockDim.x) {
+        float acc = 0.0f;
+        if (!pad)
+            for (int k = 0; k < top; ++k) {
+                const float y = ys[(size_t)row_of[(size_t)t * top + k] * W + c];
+                acc = scale_output ? fmaf(wts[(size_t)t * top + k], y, acc) : acc + y;
+            }
+        out[(size_t)t * W + c] = acc;
+    }
+}
+
+AIRUN_EXPORT int airun_moe_route(const void* h, const void* wr, int dtype, int T, int W, int E, int top, int softmax_scores,
+                                 int renorm, const int32_t* req_of_token, int32_t* ids, float* wts, int32_t* rank, int32_t* counts,
+                                 int32_t* seg, cudaStream_t stream) {
+    if (T < 0 || W <= 0 || E <= 0 || E > MOE_MAX_EXPERTS || top <= 0 || top > E || !req_of_token || !ids || !wts || !rank ||
+        !counts || !seg)
+        return AIRUN_ERR_ARG;
+    if (T == 0) return AIRUN_OK;
+    if (dtype == AIRUN_DT_F32)
+        airun_launch(moe_route_kernel<float>, dim3(T), dim3(128), 0, stream, (const float*)h, (const float*)wr, W, E, top,
+                     softmax_scores, renorm, req_of_token, ids, wts, rank, counts);
+    else if (dtype == AIRUN_DT_BF16)
+        airun_launch(moe_route_kernel<__nv_bfloat16>, dim3(T), dim3(128), 0, stream, (const __nv_bfloat16*)h,
+                     (const __nv_bfloat16*)wr, W, E, top, softmax_scores, renorm, req_of_token, ids, wts, rank, counts);
+    else
+        return AIRUN_ERR_UNSUPPORTED;
+    airun_launch(moe_offsets_kernel, dim3(1), dim3(32), 0, stream, (const int32_t*)counts, seg, E);
+    return airun_launch_status();
+}
+
+AIRUN_EXPORT int airun_moe_scatter(const void* h, int dtype, int T, int W, int top, const int32_t* ids, const float* wts,
+                                   const int32_t* rank, const int32_t* seg, int scale_input, void* xs, int32_t* row_of,
+                                   cudaStream_t stream) {
+    if (T < 0 || W <= 0 || top <= 0 || !ids || !wts || !rank || !seg || !xs || !row_of) return AIRUN_ERR_ARG;
+    if (T == 0) return AIRUN_OK;
+    if (dtype == AIRUN_DT_F32)
+        airun_launch(moe_scatter_kernel<float>, dim3(T), dim3(256), 0, stream, (const float*)h, W, top, ids, wts, rank, seg,
+                     scale_input, (float*)xs, row_of);
+    else if (dtype == AIRUN_DT_BF16)
+        airun_launch(moe_scatter_kernel<__nv_bfloat16>, dim3(T), dim3(256), 0, stream, (const __nv_bfloat16*)h, W, top, ids, wts,
+                     rank, seg, scale_input, (__nv_bfloat16*)xs, row_of);
+    else
+        return AIRUN_ERR_UNSUPPORTED;
+    return airun_launch_status();
+}
+
+AIRUN_EXPORT int airun_moe_combine(const float* ys, int T, int W, int top, const int32_t* ids, const float* wts,
+                                   const int32_t* row_of, int scale_output, float* out, cudaStream_t stream) {
+    if (T < 0 || W <= 0 || top <= 0 || !ys || !ids || !wts || !row_of || !out) return AIRUN_ERR_ARG;
+    if (T == 0) return AIRUN_OK;
+    airun_launch(moe_combine_kernel, dim3(T), dim3(256), 0, stream, ys, W, top, ids, wts, row_of, scale_output, out);
+    return airun_launch_status();
+}

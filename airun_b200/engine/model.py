@@ -18,7 +18,7 @@ from typing import Dict, List, Optional, Tuple
 import torch
 
 from ..config.base import LayerCall, ModelConfig
-from ..parts.base import make_part, part_factory
+from ..parts.base import CastActivations, make_part, part_factory
 from ..parts import embedding as _embedding_parts      # noqa: F401  (registers the embedding and head parts)
 from ..weights.loader import (DictSource, TensorSource, WeightSpec, load_tensors, random_tensors)
 
@@ -51,14 +51,16 @@ class DecoderModel:
             norm1 = make_part("norm", spec.norm, prefix=f"{p}.{names['norm1']}", **spec.norm_args, **common)
             # an arrangement with one norm (``num_norms = 1``) gets no second one; a layer without a
             # feed-forward names none (``feed_forward`` empty)
-            two_norms = getattr(part_factory("arrangement", spec.arrangement), "num_norms", 2) >= 2
+            factory = part_factory("arrangement", spec.arrangement)
+            two_norms = getattr(factory, "num_norms", 2) >= 2 and (
+                bool(spec.feed_forward) or not getattr(factory, "norm2_belongs_to_ffn", False))
             norm2 = make_part("norm", spec.norm, prefix=f"{p}.{names['norm2']}", **spec.norm_args, **common) \
                 if two_norms else None
             mixer = make_part("mixer", spec.mixer, prefix=f"{p}.{names['mixer']}", **spec.mixer_args, **common)
             ffn = make_part("feed_forward", spec.feed_forward, prefix=f"{p}.{names['ffn']}", **spec.ffn_args, **common) \
                 if spec.feed_forward else None
             self.layers.append(make_part("arrangement", spec.arrangement, norm1=norm1, mixer=mixer,
-                                         norm2=norm2, ffn=ffn, dtype=dtype))
+                                         norm2=norm2, ffn=ffn, dtype=dtype, **getattr(spec, "arrangement_args", {})))
         self.order: List[LayerCall] = list(config.execution_order())
         for c in self.order:
             if not (0 <= c.layer < len(self.layers)):
@@ -223,8 +225,11 @@ class DecoderModel:
             if next_norm is not None:
                 extra["next_norm"] = next_norm
             delta = layer.forward(ctx, x, delta, ctx.caches[ci], **extra)
-            if self.layer_hook is not None and isinstance(delta, torch.Tensor) and not torch.cuda.is_current_stream_capturing():
-                self.layer_hook(ci, x[:T] + delta[:T])
+            if self.layer_hook is not None and not torch.cuda.is_current_stream_capturing():
+                if isinstance(delta, torch.Tensor):
+                    self.layer_hook(ci, x[:T] + delta[:T])
+                elif delta is None or isinstance(delta, CastActivations):       # nothing pending: x is the stream
+                    self.layer_hook(ci, x[:T])
             if trace:           # synchronises after every block: a debugging aid, as the reference's AIRUN_TRACE_LAYERS
                 r = x[:ctx.num_tokens] if not isinstance(delta, torch.Tensor) else (x[:ctx.num_tokens] + delta[:ctx.num_tokens])
                 print(f"[airun_b200] entry {ci} layer {call.layer}: rms {float(r.pow(2).mean().sqrt()):.6f} "
@@ -234,6 +239,8 @@ class DecoderModel:
         ctx.ws = ctx.ws_pair[len(self.order) % 2]
         ctx.ws.reset()
         hsel = ctx.ws.alloc((n_want, self.H), self.dtype)
+        if isinstance(delta, CastActivations):
+            delta = None
         self.final_norm.forward(ctx, x, hsel, delta=delta, rows=want_rows[:n_want])
         logits = ctx.ws_main.alloc((n_want, self.V), torch.float32)
         self.head.forward(ctx, hsel, logits)

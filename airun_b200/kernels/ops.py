@@ -88,7 +88,8 @@ def _fn(lib_name: str, fn_name: str, argtypes, defines=None):
 def required_libraries(dtype: torch.dtype, head_dim: int):
     """(name, defines) of every library a model of this dtype and head size uses."""
     libs = [("elementwise", None), ("gemm_simt", None), ("qkv_post", None),
-            ("attention_generic", None), ("sampling", None), ("linear_attention", None), ("diff_attention", None)]
+            ("attention_generic", None), ("sampling", None), ("linear_attention", None), ("diff_attention", None),
+            ("recurrent_state", None), ("latent_attention", None), ("moe", None)]
     return libs
 
 
@@ -239,6 +240,32 @@ def glu_clamped(gate_up: torch.Tensor, out: torch.Tensor, group: int, limit: flo
              float(limit), float(slope), _stream()), "glu_clamped")
 
 
+def postnorm_add(x: torch.Tensor, y: torch.Tensor, weight: torch.Tensor, eps: float, mult: float,
+                 cast: Optional[torch.Tensor] = None) -> None:
+    """x += mult * y / rms(y) * weight row by row (the norm sits on the sub-layer's output); with ``cast`` the new x
+    is also written there in its type, as the input of the sub-layer that follows."""
+    _cuda(x, y, weight, cast)
+    _need(x.dtype == torch.float32 and x.dim() == 2 and x.is_contiguous(), "x must be contiguous float32 [T, n]")
+    T, n = x.shape
+    _need(y.dtype == torch.float32 and y.shape == x.shape and y.is_contiguous(), "y must match x")
+    _need(weight.dtype == torch.float32 and tuple(weight.shape) == (n,) and weight.is_contiguous(), "norm weight must be float32 [n]")
+    if cast is not None:
+        _need(tuple(cast.shape) == (T, n) and cast.is_contiguous(), "cast must be contiguous [T, n]")
+    f = _fn("elementwise", "airun_postnorm_add",
+            [c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_float, c_float, c_void_p])
+    _check(f(_p(x), _p(y), _p(weight), _p(cast), _dt(cast) if cast is not None else DT_F32, T, n, float(eps), float(mult),
+             _stream()), "postnorm_add")
+
+
+def cast_f32(src: torch.Tensor, out: torch.Tensor) -> None:
+    """out = src (float32) in out's type."""
+    _cuda(src, out)
+    _need(src.dtype == torch.float32 and src.is_contiguous() and out.is_contiguous() and out.numel() == src.numel(),
+          "cast_f32 takes contiguous tensors of one size")
+    f = _fn("elementwise", "airun_cast_f32", [c_void_p, c_void_p, c_int, c_longlong, c_void_p])
+    _check(f(_p(src), _p(out), _dt(out), src.numel(), _stream()), "cast_f32")
+
+
 # ---------------------------------------------------------------- gated linear attention
 def _rows_f32(t: torch.Tensor, what: str) -> None:
     _need(t.dtype == torch.float32 and t.dim() == 2 and t.stride(1) == 1, f"{what} must be float32 rows (a column slice is fine)")
@@ -295,9 +322,14 @@ def gla_recurrent(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, decay: torc
              _p(state_slots), int(num_reqs), _p(out), heads, D, Dv, float(q_scale), _p(err), _stream()), "gla_recurrent")
 
 
+GATE_SILU, GATE_SIGMOID, GATE_AS_IS = 0, 1, 2
+
+
 def gla_out_gate(o: torch.Tensor, gate: torch.Tensor, weight: Optional[torch.Tensor], eps: float, out: torch.Tensor,
-                 heads: int, Dv: int, req_of_token: torch.Tensor) -> None:
-    """out[t, h] = o[t, h] / rms(o[t, h]) * weight * silu(gate[t, h]) per head of ``Dv`` values."""
+                 heads: int, Dv: int, req_of_token: torch.Tensor, gate_act: int = GATE_SILU,
+                 weight_per_head: bool = False) -> None:
+    """out[t, h] = o[t, h] / rms(o[t, h]) * weight * f(gate[t, h]) per head of ``Dv`` values; f is silu, sigmoid
+    or the identity (``gate_act``); ``weight`` is [Dv], shared by the heads, or [heads * Dv] (``weight_per_head``)."""
     _cuda(o, gate, weight, out, req_of_token)
     T = o.shape[0]
     _need(o.dtype == torch.float32 and tuple(o.shape) == (T, heads * Dv) and o.is_contiguous(), "o must be float32 [T, heads*Dv]")
@@ -305,12 +337,41 @@ def gla_out_gate(o: torch.Tensor, gate: torch.Tensor, weight: Optional[torch.Ten
     _need(tuple(gate.shape) == (T, heads * Dv), "gate must be [T, heads*Dv]")
     _need(out.dim() == 2 and tuple(out.shape) == (T, heads * Dv) and out.stride(1) == 1, "out must be row-major [T, heads*Dv]")
     if weight is not None:
-        _need(weight.dtype == torch.float32 and tuple(weight.shape) == (Dv,) and weight.is_contiguous(), "weight must be float32 [Dv]")
+        _need(weight.dtype == torch.float32 and weight.numel() == (heads * Dv if weight_per_head else Dv)
+              and weight.is_contiguous(), "weight must be float32 [Dv] (or [heads * Dv] per head)")
     f = _fn("linear_attention", "airun_gla_out_gate",
             [c_void_p, c_void_p, c_longlong, c_void_p, c_void_p, c_int, c_longlong, c_int, c_int, c_int, c_float, c_void_p,
-             c_void_p])
+             c_int, c_int, c_void_p])
     _check(f(_p(o), _p(gate), _row_stride(gate), _p(weight), _p(out), _dt(out), _row_stride(out), T, heads, Dv, float(eps),
-             _p(req_of_token), _stream()), "gla_out_gate")
+             _p(req_of_token), int(gate_act), 1 if weight_per_head else 0, _stream()), "gla_out_gate")
+
+
+LOWRANK_POW_SIGMOID, LOWRANK_EXP_SOFTPLUS, LOWRANK_SIGMOID, LOWRANK_EXP_NEG_EXP = 0, 1, 2, 3
+
+
+def lowrank_act(low: torch.Tensor, w2: torch.Tensor, bias: Optional[torch.Tensor], out: torch.Tensor,
+                req_of_token: torch.Tensor, mode: int, in_tanh: bool = False, tau: float = 1.0,
+                group_param: Optional[torch.Tensor] = None, group: int = 0) -> None:
+    """The second half of a low-rank pair with the function that follows it, in float32:
+    z[t, c] = bias[c] + f(low[t]) . w2[c] (f = tanh with ``in_tanh``), out = sigmoid(z)^(1/tau),
+    exp(-exp(group_param[c // group]) * softplus(z)), sigmoid(z) or exp(-exp(z)) by ``mode``."""
+    _cuda(low, w2, bias, out, req_of_token, group_param)
+    _rows_f32(low, "low")
+    T, rank = low.shape
+    n = w2.shape[0]
+    _need(w2.dim() == 2 and w2.shape[1] == rank and w2.is_contiguous(), "w2 must be contiguous [n, rank]")
+    if bias is not None:
+        _need(bias.dtype == torch.float32 and bias.numel() == n and bias.is_contiguous(), "bias must be float32 [n]")
+    if group_param is not None:
+        _need(group_param.dtype == torch.float32 and group > 0 and group_param.numel() * group == n and group_param.is_contiguous(),
+              "group_param must be float32 [n / group]")
+    _need(out.dtype == torch.float32 and tuple(out.shape) == (T, n) and out.is_contiguous(), "out must be float32 [T, n]")
+    _need(req_of_token.dtype == torch.int32 and req_of_token.shape[0] >= T, "req_of_token must be int32 [T]")
+    f = _fn("linear_attention", "airun_lowrank_act",
+            [c_void_p, c_longlong, c_void_p, c_int, c_void_p, c_void_p, c_int, c_int, c_int, c_float, c_void_p, c_int, c_int,
+             c_void_p, c_int, c_void_p])
+    _check(f(_p(low), _row_stride(low), _p(w2), _dt(w2), _p(bias), _p(out), T, n, rank, float(tau), _p(req_of_token),
+             int(mode), 1 if in_tanh else 0, _p(group_param), int(group), _stream()), "lowrank_act")
 
 
 # ---------------------------------------------------------------- differential attention
@@ -389,6 +450,242 @@ def gemm_simt(a: torch.Tensor, w: torch.Tensor, out: torch.Tensor) -> None:
     _check(f(_p(a), _dt(a), _p(w), _dt(w), _p(out), _dt(out), M, N, K,
              a.stride(0) if M > 1 else max(K, a.stride(0)), w.stride(0) if N > 1 else max(K, w.stride(0)),
              out.stride(0) if M > 1 else max(N, out.stride(0)), _stream()), "gemm_simt")
+
+
+def gemm_simt_batched(a: torch.Tensor, w: torch.Tensor, out: torch.Tensor) -> None:
+    """out[:, b, :] = a[:, b, :] @ w[b]^T for every b: a [M, B, K], w [B, N, K], out [M, B, N]; a and out may be
+    views whose rows and batches are strided (column slices of wider buffers), their last axis is contiguous."""
+    _cuda(a, w, out)
+    _need(a.dim() == 3 and w.dim() == 3 and out.dim() == 3, "the batched product takes 3-d tensors")
+    M, B, K = a.shape
+    N = w.shape[1]
+    _need(w.shape[0] == B and w.shape[2] == K and tuple(out.shape) == (M, B, N), "batched product shapes do not agree")
+    _need(a.stride(2) == 1 and w.stride(2) == 1 and out.stride(2) == 1, "operands must be row-major in their last axis")
+    _need(a.dtype == w.dtype, "operands must share a type")
+    f = _fn("gemm_simt", "airun_gemm_simt_batched",
+            [c_void_p, c_int, c_void_p, c_int, c_void_p, c_int, c_int, c_int, c_int, c_longlong, c_longlong, c_longlong,
+             c_int, c_longlong, c_longlong, c_longlong, c_void_p])
+    lda = a.stride(0) if M > 1 else max(K, a.stride(0))
+    ldc = out.stride(0) if M > 1 else max(N, out.stride(0))
+    _check(f(_p(a), _dt(a), _p(w), _dt(w), _p(out), _dt(out), M, N, K, lda, w.stride(1) if N > 1 else max(K, w.stride(1)), ldc,
+             B, a.stride(1), w.stride(0), out.stride(1), _stream()), "gemm_simt_batched")
+
+
+def gemm_simt_grouped(a: torch.Tensor, w: torch.Tensor, out: torch.Tensor, seg: torch.Tensor) -> None:
+    """Rows seg[e] .. seg[e+1]-1 of a [M, K] times w[e]^T (w [E, N, K]) into the same rows of out [M, N]; ``seg`` is
+    int32 [E + 1] on the device.  Rows from seg[E] on are left as they are."""
+    _cuda(a, w, out, seg)
+    _need(a.dim() == 2 and w.dim() == 3 and out.dim() == 2 and a.is_contiguous() and w.is_contiguous() and out.is_contiguous(),
+          "the grouped product takes contiguous a [M, K], w [E, N, K], out [M, N]")
+    M, K = a.shape
+    E, N = w.shape[0], w.shape[1]
+    _need(w.shape[2] == K and tuple(out.shape) == (M, N) and a.dtype == w.dtype, "grouped product shapes or types do not agree")
+    _need(seg.dtype == torch.int32 and seg.numel() >= E + 1 and seg.is_contiguous(), "seg must be int32 [E + 1]")
+    f = _fn("gemm_simt", "airun_gemm_simt_grouped",
+            [c_void_p, c_int, c_void_p, c_int, c_void_p, c_int, c_int, c_int, c_int, c_longlong, c_longlong, c_longlong,
+             c_void_p, c_int, c_longlong, c_void_p])
+    _check(f(_p(a), _dt(a), _p(w), _dt(w), _p(out), _dt(out), M, N, K, K, K, N, _p(seg), E, N * K, _stream()),
+           "gemm_simt_grouped")
+
+
+# ---------------------------------------------------------------- recurrent mixers with a matrix state
+def short_conv(x: torch.Tensor, weight: torch.Tensor, state: torch.Tensor, tail_off: int, ctx, out: torch.Tensor,
+               n_unit_heads: int, q_heads: int, unit_dim: int, unit_eps: float, q_scale: float) -> None:
+    """out[t, c] = silu(sum_j weight[c, j] * x[t - (taps-1) + j, c]) over the rows of each request in order; rows
+    before a request's first row of this step come from state[slot, tail_off:] viewed as [taps-1, C].  The first
+    ``n_unit_heads`` heads of ``unit_dim`` channels are made unit vectors, the first ``q_heads`` of them times
+    ``q_scale``.  ``x`` float32 [T, C] (a column slice is fine), ``state`` float32 [slots, n]."""
+    _cuda(x, weight, state, out)
+    _rows_f32(x, "x")
+    T, C = x.shape
+    _need(weight.dtype == torch.float32 and weight.dim() == 2 and weight.shape[0] == C and weight.is_contiguous(),
+          "the convolution's weight must be float32 [C, taps]")
+    taps = weight.shape[1]
+    _need(state.dtype == torch.float32 and state.dim() == 2 and state.stride(1) == 1 and tail_off + (taps - 1) * C <= state.shape[1],
+          "state must be float32 [slots, n] with room for the tail")
+    _need(out.dtype == torch.float32 and tuple(out.shape) == (T, C) and out.is_contiguous(), "out must be float32 [T, C]")
+    f = _fn("recurrent_state", "airun_short_conv",
+            [c_void_p, c_longlong, c_void_p, c_int, c_void_p, c_longlong, c_longlong, c_int, c_void_p, c_void_p, c_void_p,
+             c_int, c_void_p, c_int, c_int, c_int, c_int, c_int, c_float, c_float, c_void_p, c_void_p])
+    _check(f(_p(x), _row_stride(x), _p(weight), taps, _p(state), state.stride(0), int(tail_off), state.shape[0],
+             _p(ctx.req_of_token), _p(ctx.cu_tokens), _p(ctx.state_slots), int(ctx.num_reqs), _p(out), T, C, int(n_unit_heads),
+             int(q_heads), int(unit_dim), float(unit_eps), float(q_scale), _p(ctx.err), _stream()), "short_conv")
+
+
+def token_shift(x: torch.Tensor, mu: torch.Tensor, state: torch.Tensor, prev_off: int, ctx, out: torch.Tensor) -> None:
+    """out[s, t] = x[t] + (x[t-1] - x[t]) * mu[s] in out's type; the row before a request's first row of this step
+    is state[slot, prev_off : prev_off + W].  x float32 [T, W], mu float32 [S, W], out [S, T, W]."""
+    _cuda(x, mu, state, out)
+    _need(x.dtype == torch.float32 and x.dim() == 2 and x.is_contiguous(), "x must be contiguous float32 [T, W]")
+    T, W = x.shape
+    _need(mu.dtype == torch.float32 and mu.dim() == 2 and mu.shape[1] == W and mu.is_contiguous(), "mu must be float32 [S, W]")
+    S = mu.shape[0]
+    _need(tuple(out.shape) == (S, T, W) and out.is_contiguous(), "out must be contiguous [S, T, W]")
+    _need(state.dtype == torch.float32 and state.dim() == 2 and state.stride(1) == 1 and prev_off + W <= state.shape[1],
+          "state must be float32 [slots, n] with room for the row")
+    f = _fn("recurrent_state", "airun_token_shift",
+            [c_void_p, c_void_p, c_int, c_void_p, c_longlong, c_longlong, c_int, c_void_p, c_void_p, c_void_p, c_int, c_void_p,
+             c_int, c_int, c_int, c_void_p, c_void_p])
+    _check(f(_p(x), _p(mu), S, _p(state), state.stride(0), int(prev_off), state.shape[0], _p(ctx.req_of_token), _p(ctx.cu_tokens),
+             _p(ctx.state_slots), int(ctx.num_reqs), _p(out), _dt(out), T, W, _p(ctx.err), _stream()), "token_shift")
+
+
+RECURRENCE_DELTA, RECURRENCE_WKV = 0, 1
+
+
+def recurrent_state(mode: int, q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, g: torch.Tensor, state: torch.Tensor, ctx,
+                    out: torch.Tensor, heads: int, kv_rep: int, D: int, Dv: int, beta: Optional[torch.Tensor] = None,
+                    bonus: Optional[torch.Tensor] = None, tail_src: Optional[torch.Tensor] = None, tail_off: int = 0,
+                    tail_rows: int = 0) -> None:
+    """The delta rule (RECURRENCE_DELTA: q, k [T, heads/kv_rep * D], v [T, heads*Dv], decay g [T, heads*D], beta
+    [T, heads] BEFORE its sigmoid) or the time mix with a bonus (RECURRENCE_WKV: r, k, v, decay [T, heads*D], bonus [heads, D]) over the
+    rows of every request in order, on state[slot, : heads*D*Dv] viewed as [heads, D, Dv]; out float32 [T, heads*Dv].
+    With ``tail_rows`` the last rows of (state[slot, tail_off:] as [tail_rows, C], then this step's rows of
+    ``tail_src`` [T, C]) are kept there for the next step."""
+    _cuda(q, k, v, g, state, out, beta, bonus, tail_src)
+    for t_, name in ((q, "q"), (k, "k"), (v, "v"), (g, "g")):
+        _rows_f32(t_, name)
+    T = q.shape[0]
+    _need(q.shape[1] == heads // kv_rep * D and k.shape[1] == q.shape[1] and v.shape[1] == heads * Dv and g.shape[1] == heads * D,
+          "q, k, v or the decay has the wrong width")
+    _need(state.dtype == torch.float32 and state.dim() == 2 and state.stride(1) == 1 and state.shape[1] >= heads * D * Dv,
+          "state must be float32 [slots, >= heads*D*Dv]")
+    _need(out.dtype == torch.float32 and tuple(out.shape) == (T, heads * Dv) and out.is_contiguous(), "out must be float32 [T, heads*Dv]")
+    bs = 0
+    if beta is not None:
+        _rows_f32(beta, "beta")
+        _need(beta.shape[1] == heads, "beta must be [T, heads]")
+        bs = _row_stride(beta)
+    if bonus is not None:
+        _need(bonus.dtype == torch.float32 and bonus.numel() == heads * D and bonus.is_contiguous(), "bonus must be float32 [heads, D]")
+    tw = ts = 0
+    if tail_rows:
+        _rows_f32(tail_src, "tail_src")
+        tw, ts = tail_src.shape[1], _row_stride(tail_src)
+        _need(tail_off + tail_rows * tw <= state.shape[1], "the tail does not fit the state")
+    f = _fn("recurrent_state", "airun_recurrent_state",
+            [c_int, c_void_p, c_void_p, c_void_p, c_void_p, c_longlong, c_longlong, c_longlong, c_longlong, c_void_p, c_longlong,
+             c_void_p, c_void_p, c_longlong, c_int, c_void_p, c_void_p, c_int, c_void_p, c_int, c_int, c_int, c_int, c_void_p,
+             c_longlong, c_longlong, c_int, c_int, c_void_p, c_void_p])
+    _check(f(int(mode), _p(q), _p(k), _p(v), _p(g), _row_stride(q), _row_stride(k), _row_stride(v), _row_stride(g), _p(beta), bs,
+             _p(bonus), _p(state), state.stride(0), state.shape[0], _p(ctx.cu_tokens), _p(ctx.state_slots), int(ctx.num_reqs),
+             _p(out), heads, kv_rep, D, Dv, _p(tail_src), ts, int(tail_off), int(tail_rows), tw, _p(ctx.err), _stream()),
+           "recurrent_state")
+
+
+# ---------------------------------------------------------------- attention over a cached latent
+def _latent_pool(pool: torch.Tensor, page_size: int, row: int) -> int:
+    _need(pool.is_contiguous() and pool.dim() >= 2 and pool[0].numel() == page_size * row,
+          f"a latent cache page must hold {page_size} rows of {row}")
+    return pool.shape[0]
+
+
+def latent_prepare(proj: torch.Tensor, wq: torch.Tensor, wkv: Optional[torch.Tensor], eps: float, cq: torch.Tensor,
+                   R: int, rd: int, rot_dims: int, inv_freq: Optional[torch.Tensor], rot_mult: float, cache, ctx,
+                   store: bool) -> None:
+    """cq = rmsnorm(proj[:, :q_rank]) * wq; with ``store`` the token's cache row becomes
+    [rmsnorm(proj[:, q_rank : q_rank+R]) * wkv | rotate(proj[:, q_rank+R : q_rank+R+rd])]."""
+    _cuda(proj, wq, wkv, cq, inv_freq)
+    _rows_f32(proj, "proj")
+    T, q_rank = cq.shape
+    _need(cq.is_contiguous() and proj.shape[0] == T and proj.shape[1] >= q_rank + ((R + rd) if store else 0), "proj is too narrow")
+    num_pages = max_blocks = 0
+    pool = bt = None
+    if store:
+        pool, bt = cache.pool, cache.block_table
+        num_pages = _latent_pool(pool, cache.page_size, R + rd)
+        _need(pool.dtype == cq.dtype, "the latent query and the cache pages must share a type")
+        max_blocks = bt.stride(0)
+    f = _fn("latent_attention", "airun_latent_prepare",
+            [c_void_p, c_longlong, c_void_p, c_void_p, c_float, c_void_p, c_int, c_int, c_int, c_int, c_int, c_void_p, c_float,
+             c_void_p, c_void_p, c_int, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int, c_void_p, c_void_p])
+    _check(f(_p(proj), _row_stride(proj), _p(wq), _p(wkv), float(eps), _p(cq), _dt(cq), q_rank, R, rd, rot_dims, _p(inv_freq),
+             float(rot_mult), _p(pool), _p(bt), max_blocks, _p(ctx.positions), _p(ctx.req_of_token), T, int(ctx.num_reqs),
+             num_pages, int(cache.page_size), 1 if store else 0, _p(ctx.err), _stream()), "latent_prepare")
+
+
+def latent_query(q: torch.Tensor, qn: torch.Tensor, qlat: torch.Tensor, H: int, D: int, R: int, rd: int, rot_dims: int,
+                 inv_freq: Optional[torch.Tensor], rot_mult: float, ctx) -> None:
+    """q float32 [T, H*(D+rd)] -> qn [T, H*D] (the unrotated parts) and the rotated parts, turned by each token's
+    position, into qlat[t, h, R:] (qlat [T, H*(R+rd)])."""
+    _cuda(q, qn, qlat, inv_freq)
+    T = q.shape[0]
+    _need(q.dtype == torch.float32 and tuple(q.shape) == (T, H * (D + rd)) and q.is_contiguous(), "q must be float32 [T, H*(D+rd)]")
+    _need(tuple(qn.shape) == (T, H * D) and qn.is_contiguous() and tuple(qlat.shape) == (T, H * (R + rd)) and qlat.is_contiguous()
+          and qn.dtype == qlat.dtype, "qn / qlat must be contiguous [T, H*D] / [T, H*(R+rd)] of one type")
+    f = _fn("latent_attention", "airun_latent_query",
+            [c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_void_p, c_float, c_void_p, c_void_p,
+             c_void_p])
+    _check(f(_p(q), _p(qn), _p(qlat), _dt(qn), T, H, D, R, rd, rot_dims, _p(inv_freq), float(rot_mult), _p(ctx.positions),
+             _p(ctx.req_of_token), _stream()), "latent_query")
+
+
+def latent_attention(qlat: torch.Tensor, out: torch.Tensor, cache, ctx, H: int, R: int, rd: int, scale: float, window: int,
+                     sink: Optional[torch.Tensor]) -> None:
+    """out[t, h] = sum_j p_j c_j over the cached rows [c | kr] each token sees (0 <= pos - j < window, or all with
+    window 0), p the softmax of scale * qlat[t, h] . [c_j | kr_j] with exp(sink[h]) added to its denominator."""
+    _cuda(qlat, out, sink)
+    T = qlat.shape[0]
+    _need(tuple(qlat.shape) == (T, H * (R + rd)) and qlat.is_contiguous() and tuple(out.shape) == (T, H * R) and out.is_contiguous()
+          and out.dtype == qlat.dtype, "qlat / out must be contiguous [T, H*(R+rd)] / [T, H*R] of one type")
+    num_pages = _latent_pool(cache.pool, cache.page_size, R + rd)
+    _need(cache.pool.dtype == qlat.dtype, "the query and the cache pages must share a type")
+    _need(R + rd <= 640, "cached rows above 640 elements are beyond the kernel")
+    if sink is not None:
+        _need(sink.dtype == torch.float32 and sink.numel() == H and sink.is_contiguous(), "sink must be float32 [H]")
+    f = _fn("latent_attention", "airun_latent_attention",
+            [c_void_p, c_void_p, c_int, c_void_p, c_void_p, c_int, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int, c_int,
+             c_int, c_float, c_int, c_void_p, c_void_p, c_void_p])
+    _check(f(_p(qlat), _p(out), _dt(qlat), _p(cache.pool), _p(cache.block_table), cache.block_table.stride(0), _p(ctx.positions),
+             _p(ctx.req_of_token), T, int(ctx.num_reqs), num_pages, int(cache.page_size), H, R, rd, float(scale), int(window),
+             _p(sink), _p(ctx.err), _stream()), "latent_attention")
+
+
+# ---------------------------------------------------------------- routed experts
+def moe_route(h: torch.Tensor, w_router: torch.Tensor, top: int, softmax_scores: bool, renorm: bool, req_of_token: torch.Tensor,
+              ids: torch.Tensor, wts: torch.Tensor, rank: torch.Tensor, counts: torch.Tensor, seg: torch.Tensor) -> None:
+    """ids / wts [T, top]: every token's ``top`` experts by score (sigmoid or softmax of h @ w_router^T, float32) and
+    their weights; rank [T, top]: the row's place among its expert's rows; seg [E + 1]: where each expert's rows begin.
+    ``counts`` (int32 [E]) must be zero on entry."""
+    _cuda(h, w_router, req_of_token, ids, wts, rank, counts, seg)
+    T, W = h.shape
+    E = w_router.shape[0]
+    _need(h.is_contiguous() and w_router.is_contiguous() and w_router.shape[1] == W and h.dtype == w_router.dtype,
+          "h [T, W] and the router [E, W] must be contiguous and of one type")
+    _need(E <= 1024 and 1 <= top <= E, "1 to 1024 experts, top of them a token")
+    for t_, dt in ((ids, torch.int32), (wts, torch.float32), (rank, torch.int32)):
+        _need(t_.dtype == dt and t_.numel() >= T * top and t_.is_contiguous(), "ids / wts / rank must be [T, top]")
+    _need(counts.dtype == torch.int32 and counts.numel() >= E and seg.dtype == torch.int32 and seg.numel() >= E + 1,
+          "counts / seg must be int32 [E] / [E + 1]")
+    f = _fn("moe", "airun_moe_route",
+            [c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p,
+             c_void_p, c_void_p])
+    _check(f(_p(h), _p(w_router), _dt(h), T, W, E, int(top), 1 if softmax_scores else 0, 1 if renorm else 0, _p(req_of_token),
+             _p(ids), _p(wts), _p(rank), _p(counts), _p(seg), _stream()), "moe_route")
+
+
+def moe_scatter(h: torch.Tensor, top: int, ids, wts, rank, seg, scale_input: bool, xs: torch.Tensor, row_of: torch.Tensor) -> None:
+    """xs[seg[e] + rank] = h[t] (times the weight with ``scale_input``) for each of the token's experts; row_of [T, top]
+    keeps the row."""
+    _cuda(h, xs, row_of)
+    T, W = h.shape
+    _need(h.is_contiguous() and xs.is_contiguous() and tuple(xs.shape) == (T * top, W) and xs.dtype == h.dtype,
+          "xs must be contiguous [T*top, W] of h's type")
+    _need(row_of.dtype == torch.int32 and row_of.numel() >= T * top, "row_of must be int32 [T, top]")
+    f = _fn("moe", "airun_moe_scatter",
+            [c_void_p, c_int, c_int, c_int, c_int, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_void_p, c_void_p, c_void_p])
+    _check(f(_p(h), _dt(h), T, W, int(top), _p(ids), _p(wts), _p(rank), _p(seg), 1 if scale_input else 0, _p(xs), _p(row_of),
+             _stream()), "moe_scatter")
+
+
+def moe_combine(ys: torch.Tensor, top: int, ids, wts, row_of, scale_output: bool, out: torch.Tensor) -> None:
+    """out[t] = sum over the token's experts, in the order chosen, of ys[row] (times the weight with ``scale_output``)."""
+    _cuda(ys, out)
+    T, W = out.shape
+    _need(ys.dtype == torch.float32 and ys.is_contiguous() and tuple(ys.shape) == (T * top, W) and out.dtype == torch.float32
+          and out.is_contiguous(), "ys / out must be contiguous float32 [T*top, W] / [T, W]")
+    f = _fn("moe", "airun_moe_combine", [c_void_p, c_int, c_int, c_int, c_void_p, c_void_p, c_void_p, c_int, c_void_p, c_void_p])
+    _check(f(_p(ys), T, W, int(top), _p(ids), _p(wts), _p(row_of), 1 if scale_output else 0, _p(out), _stream()), "moe_combine")
 
 
 # ---------------------------------------------------------------- attention

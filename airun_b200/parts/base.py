@@ -62,15 +62,17 @@ class PagedKVSpec:
     """Keys and values of every (or the last ``window``) token(s), in pages.  ``head_dim`` is the size of a
     key row of one KV head; a value row has ``value_dim`` elements when that differs (0: the same).  A page
     holds the keys of all heads, then the values: [kv_heads, page_size, head_dim] + [kv_heads, page_size,
-    value_dim], which with equal sizes is [2, kv_heads, page_size, head_dim]."""
+    value_dim], which with equal sizes is [2, kv_heads, page_size, head_dim].  With ``values`` False a token has
+    no value rows at all (a cached latent that serves as key and value): a page is [kv_heads, page_size, head_dim]."""
     num_kv_heads: int
     head_dim: int
     window: int = 0          # 0: all tokens are kept
     value_dim: int = 0       # 0: values have head_dim elements too
+    values: bool = True      # False: nothing but the key rows is cached
 
     @property
     def v_dim(self) -> int:
-        return self.value_dim or self.head_dim
+        return (self.value_dim or self.head_dim) if self.values else 0
 
     def elements_per_token(self) -> int:
         return self.num_kv_heads * (self.head_dim + self.v_dim)
@@ -93,6 +95,13 @@ class NormedActivations:
     ssq: torch.Tensor
     eps: float
     size: int
+
+
+@dataclass
+class CastActivations:
+    """What a block whose sub-layers read the residual stream itself hands to the next one: the stream is up to
+    date (nothing is pending) and ``h`` holds it in the compute type already."""
+    h: torch.Tensor
 
 
 @dataclass

@@ -18,7 +18,7 @@ from typing import Dict, List, Optional
 import torch
 
 from ..weights.loader import WeightSpec
-from .base import FeedForward, Mixer, Norm, NormedActivations, Part, ResidualSink, register_part
+from .base import CastActivations, FeedForward, Mixer, Norm, NormedActivations, Part, ResidualSink, register_part
 
 
 class PreNormBlock(Part):
@@ -161,3 +161,72 @@ class ParallelBlock(Part):
 
 
 register_part("arrangement", "parallel", ParallelBlock)
+
+
+class PostNormBlock(Part):
+    """The norm sits on each sub-layer's OUTPUT: x += m * norm1(mixer(x)), then x += m * norm2(ffn(x)).  The
+    sub-layers read the residual stream itself (in the compute type: a bfloat16 copy when serving in bfloat16, x as
+    it is on the 32-bit path); ``residual_mult`` m scales what is added.  The feed-forward may be absent, and then
+    so is norm2.  Norm and add are one kernel, which also writes the copy the next sub-layer reads; nothing is left
+    pending for the next block, which gets that copy as CastActivations.  A mixer that declares
+    ``input_float32 = True`` is given x in float32 whatever the compute type.  The norms must offer ``fusable()``
+    (weight, eps) of a root-mean-square norm."""
+    norm2_belongs_to_ffn = True
+
+    def __init__(self, norm1: Norm, mixer: Mixer, norm2: Optional[Norm], ffn: Optional[FeedForward], dtype: torch.dtype,
+                 residual_mult: float = 1.0):
+        self.norm1, self.mixer, self.norm2, self.ffn, self.dtype = norm1, mixer, norm2, ffn, dtype
+        self.mult = float(residual_mult)
+        for n in (norm1, norm2):
+            if n is not None and not hasattr(n, "fusable"):
+                raise ValueError("a post-norm block needs root-mean-square norms (parts with fusable())")
+
+    def parts(self):
+        return tuple(p for p in (self.norm1, self.mixer, self.norm2, self.ffn) if p is not None)
+
+    def weight_specs(self) -> List[WeightSpec]:
+        return [s for p in self.parts() for s in p.weight_specs()]
+
+    def load_weights(self, tensors: Dict[str, torch.Tensor]) -> None:
+        for p in self.parts():
+            p.load_weights(tensors)
+
+    def cache_spec(self):
+        return self.mixer.cache_spec()
+
+    def device_driven(self) -> bool:
+        return all(getattr(p, "device_driven", False) for p in self.parts())
+
+    def graph_safe(self) -> bool:
+        return all(getattr(p, "graph_safe", True) for p in self.parts())
+
+    def accepts_normed(self) -> bool:
+        return False
+
+    def forward(self, ctx, x: torch.Tensor, pending, cache, next_norm: Optional[Norm] = None):
+        from ..kernels import ops
+        T, H = x.shape
+        f32 = self.dtype == torch.float32
+        if isinstance(pending, torch.Tensor):           # a block of another arrangement left its delta to be added
+            ops.add_rows(x, delta=pending)
+            pending = None
+        if f32 or getattr(self.mixer, "input_float32", False):
+            h = x
+        elif isinstance(pending, CastActivations):
+            h = pending.h
+        else:
+            h = ctx.ws.alloc((T, H), self.dtype)
+            ops.cast_f32(x, h)
+        y = self.mixer.forward(ctx, h, cache)
+        cast = None if f32 else ctx.ws.alloc((T, H), self.dtype)
+        w, eps = self.norm1.fusable()
+        ops.postnorm_add(x, y, w, eps, self.mult, cast=cast)
+        if self.ffn is not None:
+            y = self.ffn.forward(ctx, x if f32 else cast)
+            cast = None if f32 else ctx.ws.alloc((T, H), self.dtype)
+            w, eps = self.norm2.fusable()
+            ops.postnorm_add(x, y, w, eps, self.mult, cast=cast)
+        return None if f32 else CastActivations(cast)
+
+
+register_part("arrangement", "post_norm", PostNormBlock)

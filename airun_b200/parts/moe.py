@@ -1,0 +1,96 @@
+"""Routed experts: a feed-forward made of many small gated units of which every token uses a few.
+
+    z = Wr h  (float32),   s = sigmoid(z)  (or softmax(z) with ``scores="softmax"``)
+    the ``top`` experts with the largest s are chosen (equal scores: the lower id)
+    weight_e = s_e, divided by the sum over the chosen ones when ``renormalize``
+    out = sum_e expert_e(weight_e * h)          (``weight_on="input"``: the weight scales what the expert reads)
+    out = sum_e weight_e * expert_e(h)          (``weight_on="output"``)
+    expert_e(x) = Wdown_e ( silu(Wgate_e x) * (Wup_e x) )
+
+Everything is decided on the device: a step's rows are sorted by expert into segments of one buffer and every
+expert's matrices meet only their own segment (csrc/moe.cu, the grouped product of csrc/gemm_simt.cu), so the part
+launches the same kernels for every batch and is replayed from CUDA graphs like the dense parts.  A token's result
+depends on its own row alone.  Tensors: ``<prefix>.router`` and ``<prefix>.e<i>.{gate,up,down}``.
+"""
+from __future__ import annotations
+
+from typing import Dict, List, Optional
+
+import torch
+
+from ..kernels import ops
+from ..weights.loader import WeightSpec
+from .base import FeedForward, register_part
+from .mlp import INTERLEAVE
+
+
+class RoutedExperts(FeedForward):
+    device_driven = True
+
+    def __init__(self, prefix: str, hidden_size: int, intermediate_size: int, num_experts: int, top: int,
+                 scores: str = "sigmoid", renormalize: bool = False, weight_on: str = "input",
+                 dtype: torch.dtype = torch.bfloat16, device=None, names: Optional[Dict[str, str]] = None):
+        self.prefix, self.H, self.I = prefix, int(hidden_size), int(intermediate_size)
+        self.E, self.top = int(num_experts), int(top)
+        if not (1 <= self.top <= self.E <= 1024):
+            raise ValueError(f"1 to 1024 experts and 1 to all of them a token, found {num_experts} and {top}")
+        if scores not in ("sigmoid", "softmax") or weight_on not in ("input", "output"):
+            raise ValueError("scores is 'sigmoid' or 'softmax', weight_on is 'input' or 'output'")
+        self.softmax, self.renorm, self.on_input = scores == "softmax", bool(renormalize), weight_on == "input"
+        self.dtype, self.device = dtype, device
+        self.group = INTERLEAVE if self.I % INTERLEAVE == 0 else self.I
+        n = dict(router="router", expert="e{e}", gate="gate", up="up", down="down")
+        n.update(names or {})
+        self.n = n
+        self.w_router = self.w_gu = self.w_down = self.counts = None
+
+    def _name(self, e: int, which: str) -> str:
+        return f"{self.prefix}.{self.n['expert'].format(e=e)}.{self.n[which]}"
+
+    def weight_specs(self) -> List[WeightSpec]:
+        specs = [WeightSpec(f"{self.prefix}.{self.n['router']}", (self.E, self.H))]
+        for e in range(self.E):
+            specs += [WeightSpec(self._name(e, "gate"), (self.I, self.H)), WeightSpec(self._name(e, "up"), (self.I, self.H)),
+                      WeightSpec(self._name(e, "down"), (self.H, self.I))]
+        return specs
+
+    def load_weights(self, tensors: Dict[str, torch.Tensor]) -> None:
+        g, nb = self.group, self.I // self.group
+        self.w_router = tensors.pop(f"{self.prefix}.{self.n['router']}")
+        gus, downs = [], []
+        for e in range(self.E):
+            gate, up = tensors.pop(self._name(e, "gate")), tensors.pop(self._name(e, "up"))
+            # gate and up rows alternate in blocks of ``group``, as in the dense gated units
+            gus.append(torch.stack([gate.view(nb, g, self.H), up.view(nb, g, self.H)], dim=1).reshape(2 * self.I, self.H))
+            downs.append(tensors.pop(self._name(e, "down")))
+        self.w_gu = torch.stack(gus, dim=0).contiguous()          # [E, 2I, H]
+        self.w_down = torch.stack(downs, dim=0).contiguous()      # [E, H, I]
+        self.counts = torch.zeros(self.E, dtype=torch.int32, device=self.w_router.device)
+
+    def forward(self, ctx, h: torch.Tensor, sink=None):
+        T, ws, top = h.shape[0], ctx.ws, self.top
+        M = T * top
+        ids, rank, row_of = (ws.alloc((T, top), torch.int32) for _ in range(3))
+        wts = ws.alloc((T, top), torch.float32)
+        seg = ws.alloc((self.E + 1,), torch.int32)
+        self.counts.zero_()
+        ops.moe_route(h, self.w_router, top, self.softmax, self.renorm, ctx.req_of_token, ids, wts, rank, self.counts, seg)
+        xs = ws.alloc((M, self.H), self.dtype)
+        ops.moe_scatter(h, top, ids, wts, rank, seg, self.on_input, xs, row_of)
+        gu = ws.alloc((M, 2 * self.I), torch.float32)
+        grouped_linear(ctx, xs, self.w_gu, gu, seg)
+        act = ws.alloc((M, self.I), self.dtype)
+        ops.swiglu(gu, act, self.group)
+        ys = ws.alloc((M, self.H), torch.float32)
+        grouped_linear(ctx, act, self.w_down, ys, seg)
+        delta = ws.alloc((T, self.H), torch.float32)
+        ops.moe_combine(ys, top, ids, wts, row_of, not self.on_input, delta)
+        return delta
+
+
+def grouped_linear(ctx, x: torch.Tensor, w: torch.Tensor, out: torch.Tensor, seg: torch.Tensor) -> None:
+    """Rows seg[e] .. seg[e+1]-1 of x times w[e]^T: x [M, K], w [E, N, K], out [M, N], seg int32 [E+1] on the device."""
+    ops.gemm_simt_grouped(x, w, out, seg)
+
+
+register_part("feed_forward", "routed_experts", RoutedExperts)

@@ -22,7 +22,8 @@ class RMSNorm(Norm):
     def __init__(self, prefix: str, size: int, eps: float, dtype=None, device=None,
                  weight_name: str = "weight"):
         self.prefix, self.size, self.eps = prefix, int(size), float(eps)
-        self.name = f"{prefix}.{weight_name}" if prefix else weight_name
+        # weight_name "": the tensor is called by the prefix itself
+        self.name = f"{prefix}.{weight_name}" if (prefix and weight_name) else (prefix or weight_name)
         self.weight: Optional[torch.Tensor] = None
 
     def weight_specs(self) -> List[WeightSpec]:

@@ -51,3 +51,42 @@ class NoPosition(PositionEncoding):
 register_part("position", "rotary_neox", RotaryNeox)
 register_part("position", "rotary_interleaved", RotaryInterleaved)
 register_part("position", "none", NoPosition)
+
+
+class RotaryScaledInterleaved(RotaryInterleaved):
+    """Neighbouring dimensions (2i, 2i + 1) with frequencies stretched for longer contexts than the model was
+    trained on: with ``scaling`` = {factor, original, fast, slow}, a pair that turns more than ``fast`` times over
+    ``original`` positions keeps its frequency, one that turns fewer than ``slow`` times has it divided by
+    ``factor``, and the pairs between are blended linearly by their index,
+
+        at(t) = dims * ln(original / (2 pi t)) / (2 ln theta),  lo = max(floor(at(fast)), 0),
+        hi = min(ceil(at(slow)), dims - 1),  ramp_i = clamp((i - lo) / max(hi - lo, 0.001), 0, 1),
+        f_i' = f_i / factor * ramp_i + f_i * (1 - ramp_i);
+
+    cos and sin are both multiplied by ``mult`` = 0.1 ln(factor) + 1.  Without ``scaling`` it is RotaryInterleaved
+    with mult 1.  Everything is computed once in double precision and rounded to float32."""
+
+    def __init__(self, prefix: str = "", rotary_dim: int = 0, theta: float = 10000.0, scaling: Optional[dict] = None,
+                 dtype=None, device=None):
+        import math
+        super().__init__(prefix, rotary_dim, theta, dtype, device)
+        self.mult = 1.0
+        if scaling:
+            factor, original = float(scaling["factor"]), float(scaling["original"])
+            fast, slow = float(scaling["fast"]), float(scaling["slow"])
+            if not (factor > 0 and original > 0 and fast > 0 and slow > 0):
+                raise ValueError("factor, original, fast and slow of a rotary scaling must be positive")
+
+            def at(turns: float) -> float:
+                return rotary_dim * math.log(original / (2 * math.pi * turns)) / (2 * math.log(self.theta))
+
+            lo = max(math.floor(at(fast)), 0)
+            hi = min(math.ceil(at(slow)), rotary_dim - 1)
+            i = torch.arange(0, rotary_dim // 2, dtype=torch.float64)
+            f = torch.pow(torch.tensor(self.theta, dtype=torch.float64), -2.0 * i / rotary_dim)
+            ramp = torch.clamp((i - lo) / max(hi - lo, 0.001), 0.0, 1.0)
+            self.inv_freq = (f / factor * ramp + f * (1.0 - ramp)).to(torch.float32).to(device)
+            self.mult = 0.1 * math.log(factor) + 1.0
+
+
+register_part("position", "rotary_scaled_interleaved", RotaryScaledInterleaved)
