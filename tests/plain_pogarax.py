@@ -187,7 +187,13 @@ def plain_latent_kv(h, W, p: str, m: dict, eps: float, positions, rnd: Rounding 
     return _r(rnd, c), _r(rnd, kr)
 
 
-def plain_latent_attention(h, W, p: str, m: dict, eps: float, c, kr, positions, rnd: Rounding = None):
+def plain_latent_attention(h, W, p: str, m: dict, eps: float, c, kr, positions, rnd: Rounding = None,
+                           in_latent_space: Optional[bool] = None):
+    """``in_latent_space`` (the default when ``rnd`` is given): the same sums associated the other way, with the
+    query's unrotated part carried through Wuk^T and Wuv applied to the weighted sum of latents, which is where the
+    bfloat16 engine rounds."""
+    if in_latent_space is None:
+        in_latent_space = rnd is not None
     T = h.shape[0]
     H, D, rd, Dv = m["heads"], m["dim"], m["rot_dim"], m["vdim"]
     cq = _r(rnd, plain_rmsnorm(h @ W[p + ".dq"].T, W[p + ".dq.norm"], eps))
@@ -200,10 +206,16 @@ def plain_latent_attention(h, W, p: str, m: dict, eps: float, c, kr, positions, 
     v = (c @ W[p + ".uv"].T).view(T, H, Dv)
     vis = plain_window(T, (m.get("mask") or {}).get("size", 0))
     out = torch.zeros(T, H, Dv, dtype=h.dtype)
+    wuk, wuv = W[p + ".uk"].view(H, D, -1), W[p + ".uv"].view(H, Dv, -1)
     for hd in range(H):
-        s = (qn[:, hd] @ kn[:, hd].T + qr[:, hd] @ kr.T) * m["scale"]
+        if in_latent_space:
+            qa = _r(rnd, _r(rnd, qn[:, hd]) @ wuk[hd])                        # [T, R]
+            s = (qa @ c.T + _r(rnd, qr[:, hd]) @ kr.T) * m["scale"]
+        else:
+            s = (qn[:, hd] @ kn[:, hd].T + qr[:, hd] @ kr.T) * m["scale"]
         s = s.masked_fill(~vis, -math.inf)
-        out[:, hd] = plain_sink_softmax(s, float(W[p + ".sink"][hd])) @ v[:, hd]
+        pr = plain_sink_softmax(s, float(W[p + ".sink"][hd]))
+        out[:, hd] = _r(rnd, pr @ c) @ wuv[hd].T if in_latent_space else pr @ v[:, hd]
     return _r(rnd, out.reshape(T, H * Dv)) @ W[p + ".o"].T
 
 
@@ -239,7 +251,7 @@ def plain_wkv(h, W, p: str, m: dict, eps: float, rnd: Rounding = None):
 # ----------------------------------------------------------------------------- the model
 def plain_forward(cfg: dict, W: Dict[str, torch.Tensor], tokens: List[int], dtype=torch.float64, rnd: Rounding = None,
                   residuals: Optional[list] = None) -> torch.Tensor:
-    """Logits [T, vocab] of the whole sequence."""
+    """Logits [T, vocab] of the whole sequence.  ``residuals`` collects the stream after every layer."""
     W = {n: t.to(dtype) for n, t in W.items()}
     eps, mult = cfg["norm"]["eps"], cfg.get("residual_mult", 1.0)
     T = len(tokens)
@@ -278,3 +290,129 @@ def plain_greedy(cfg, W, prompt: List[int], n_new: int) -> List[int]:
     for _ in range(n_new):
         toks.append(int(torch.argmax(plain_forward(cfg, W, toks)[-1])))
     return toks[len(prompt):]
+
+
+# ----------------------------------------------------------------------------- configurations and weights
+def dense(ff: int) -> dict:
+    return dict(kind="dense", ff=ff)
+
+
+def moe(ff: int, experts: int, top: int) -> dict:
+    return dict(kind="moe", expert=dict(ff=ff), router=dict(experts=experts, top=top))
+
+
+def delta_layer(heads, kv_heads, dim, vdim, conv, mlp=None) -> dict:
+    return dict(type="channel_delta", mixer=dict(heads=heads, kv_heads=kv_heads, dim=dim, vdim=vdim, conv=conv), mlp=mlp)
+
+
+def latent_layer(heads, dim, rot_dim, vdim, q_rank, kv_rank, window=None, scale=None, base=10000.0, scaling=None,
+                 kv_from=None, mlp=None) -> dict:
+    m = dict(heads=heads, dim=dim, rot_dim=rot_dim, vdim=vdim, q_rank=q_rank, kv_rank=kv_rank,
+             scale=scale if scale is not None else (dim + rot_dim) ** -0.5, rot=dict(dims=rot_dim, base=base))
+    if scaling is not None:
+        m["rot"]["scaling"] = dict(factor=scaling[0], original=scaling[1], fast=scaling[2], slow=scaling[3])
+    if window is not None:
+        m["mask"] = dict(size=window)
+    if kv_from is not None:
+        m["kv_from"] = kv_from
+    return dict(type="latent_attention", mixer=m, mlp=mlp)
+
+
+def wkv_layer(heads, dim, mlp=None) -> dict:
+    return dict(type="wkv", mixer=dict(heads=heads, dim=dim), mlp=mlp)
+
+
+def all_experts(cfg: dict) -> dict:
+    """The same model with every router choosing ALL its experts (the scores still weigh them): a choice that no
+    rounding can change, for comparisons in reduced precision."""
+    out = json.loads(json.dumps(cfg))
+    for l in out["layers"]:
+        if l.get("mlp") and l["mlp"]["kind"] == "moe":
+            l["mlp"]["router"]["top"] = l["mlp"]["router"]["experts"]
+    return out
+
+
+def make_config(vocab, width, layers, eps=1e-5, mult=0.7) -> dict:
+    return dict(architecture="Pogarax", vocab=vocab, width=width, norm=dict(eps=eps), residual_mult=mult, layers=layers)
+
+
+def tensor_shapes(cfg: dict, ranks=(6, 5, 4)) -> Dict[str, tuple]:
+    """name -> shape of every tensor of a model; ``ranks``: of the delta rule's decay pair and gate pair, and of the
+    time mix's decay pair."""
+    Wd, shapes = cfg["width"], {}
+    shapes["embed"] = (cfg["vocab"], Wd)
+    shapes["head"] = (cfg["vocab"], Wd)
+    shapes["final.norm"] = (Wd,)
+    for i, l in enumerate(cfg["layers"]):
+        p, m = f"l{i}", l["mixer"]
+        shapes[p + ".norm1"] = (Wd,)
+        x = p + ".mix."
+        if l["type"] == "channel_delta":
+            kd, vd, hd = m["kv_heads"] * m["dim"], m["heads"] * m["vdim"], m["heads"] * m["dim"]
+            shapes.update({x + "q": (kd, Wd), x + "k": (kd, Wd), x + "v": (vd, Wd), x + "q.conv": (kd, m["conv"]),
+                           x + "k.conv": (kd, m["conv"]), x + "v.conv": (vd, m["conv"]), x + "b": (m["heads"], Wd),
+                           x + "A_log": (m["heads"],), x + "norm": (m["vdim"],), x + "a1": (ranks[0], Wd), x + "a2": (hd, ranks[0]),
+                           x + "dt_bias": (hd,), x + "g1": (ranks[1], Wd), x + "g2": (vd, ranks[1]), x + "o": (Wd, vd)})
+        elif l["type"] == "latent_attention":
+            H, D, rd, Dv, R = m["heads"], m["dim"], m["rot_dim"], m["vdim"], m["kv_rank"]
+            shapes.update({x + "dq": (m["q_rank"], Wd), x + "dq.norm": (m["q_rank"],), x + "uq": (H * (D + rd), m["q_rank"]),
+                           x + "uk": (H * D, R), x + "uv": (H * Dv, R), x + "sink": (H,), x + "o": (Wd, H * Dv)})
+            if "kv_from" not in m:
+                shapes.update({x + "dkv": (R + rd, Wd), x + "dkv.norm": (R,)})
+        else:
+            hd = m["heads"] * m["dim"]
+            shapes.update({x + f"mu.{s}": (Wd,) for s in "rkvgw"})
+            shapes.update({x + s: (hd, Wd) for s in "rkvg"})
+            shapes.update({x + "w1": (ranks[2], Wd), x + "w2": (hd, ranks[2]), x + "w0": (hd,), x + "u": (m["heads"], m["dim"]),
+                           x + "norm": (hd,), x + "o": (Wd, hd)})
+        mlp = l.get("mlp")
+        if mlp:
+            shapes[p + ".norm2"] = (Wd,)
+            if mlp["kind"] == "dense":
+                shapes.update({p + ".mlp.gate": (mlp["ff"], Wd), p + ".mlp.up": (mlp["ff"], Wd), p + ".mlp.down": (Wd, mlp["ff"])})
+            else:
+                ff = mlp["expert"]["ff"]
+                shapes[p + ".mlp.router"] = (mlp["router"]["experts"], Wd)
+                for e in range(mlp["router"]["experts"]):
+                    shapes.update({f"{p}.mlp.e{e}.gate": (ff, Wd), f"{p}.mlp.e{e}.up": (ff, Wd), f"{p}.mlp.e{e}.down": (Wd, ff)})
+    return shapes
+
+
+def random_weights(cfg: dict, seed: int, ranks=(6, 5, 4), gain: float = 1.0) -> Dict[str, torch.Tensor]:
+    """Weights large enough that every mechanism moves the logits: matrices N(0, gain^2 / fan_in), norm weights
+    near 1, decays spread between slow and fast, sinks, bonuses and blends of a visible size; all rounded to
+    bfloat16, the file's type."""
+    g = torch.Generator().manual_seed(seed)
+    W = {}
+    for name, shape in tensor_shapes(cfg, ranks).items():
+        leaf = name.rsplit(".", 1)[-1]
+        if name.endswith(".conv"):
+            t = 0.6 * torch.randn(shape, generator=g)
+        elif ".mu." in name:
+            t = torch.rand(shape, generator=g)
+        elif len(shape) == 2 and leaf != "u":
+            std = 1.0 if name == "embed" else gain / math.sqrt(shape[1])
+            if leaf in ("a2", "g2", "w2", "router"):
+                std *= 2.0
+            t = torch.randn(shape, generator=g) * std
+        elif leaf.startswith("norm") or name == "final.norm":
+            t = 1.0 + 0.2 * torch.randn(shape, generator=g)
+        elif leaf == "A_log":
+            t = torch.randn(shape, generator=g) - 1.0
+        elif leaf == "w0":
+            t = torch.randn(shape, generator=g) - 2.0
+        elif leaf == "sink":
+            t = torch.randn(shape, generator=g) + 0.5
+        else:                                               # dt_bias, u
+            t = 0.5 * torch.randn(shape, generator=g)
+        W[name] = t.to(torch.bfloat16)
+    return W
+
+
+def write_folder(folder: str, cfg: dict, W: Dict[str, torch.Tensor]) -> str:
+    from safetensors.torch import save_file
+    os.makedirs(folder, exist_ok=True)
+    with open(os.path.join(folder, "config.json"), "w") as f:
+        json.dump(cfg, f)
+    save_file({n: t.contiguous() for n, t in W.items()}, os.path.join(folder, "model.safetensors"))
+    return folder
