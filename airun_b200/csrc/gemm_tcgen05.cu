@@ -190,6 +190,10 @@ struct GemmParams {
     int cluster_reduce;           // the ksplit CTAs of a tile are one cluster and add their slices through
                                   // distributed shared memory instead of the scratch
     float glu_limit, glu_slope;   // EPI_SWIGLU: 0, 0 for SwiGLU; a limit > 0 for the clamped gated unit
+    // grouped form of the persistent kernel: the rows of A are cut into n_seg segments (seg[e] .. seg[e + 1] - 1, device
+    // memory) and segment e is multiplied by rows e * b_rows .. of the B operand (one matrix per segment, stacked)
+    const int32_t* seg;
+    int n_seg;
 };
 
 template <int BN, int STAGES>
@@ -632,13 +636,22 @@ __global__ __launch_bounds__(GEMM_THREADS, 1) void gemm_tcgen05_kernel(
 // weight tile).  The stage ring runs on across tiles, and the accumulator is double-buffered in
 // tensor memory (2 x 256 columns): while the epilogue warps drain tile i, the MMA thread is already
 // filling tile i + 1.  Normal mode, BN = 256, no K slices.
+//
+// GROUPED: the rows of A are segments, each with a B matrix of its own (the experts of a routed feed-forward whose
+// rows have been sorted by expert).  Where the segments lie is only known on the device, so every CTA first lists
+// the row tiles of all segments in shared memory (first row, end of the segment, segment) and then walks
+// (row tile, column tile) pairs as above; a tile's rows beyond its segment's end are computed and not stored.  The
+// launch is sized for the most row tiles any cut can have, ceil(rows / 128) + segments.
 #define PBN 256
 #define PSTAGES 4
-template <int EPI>
+#define GROUP_MAX_TILES 1024
+#define GROUP_MAX_SEGS 1024
+template <int EPI, bool GROUPED>
 __global__ __launch_bounds__(GEMM_THREADS, 1) void gemm_tcgen05_persistent_kernel(
     const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b, const GemmParams p,
     int m_tiles, int n_tiles) {
     pdl_trigger();
+    __shared__ int s_tab[GROUPED ? 3 * GROUP_MAX_TILES : 1], s_first[GROUPED ? GROUP_MAX_SEGS + 1 : 1];
     using L = SmemLayout<PBN, PSTAGES>;
     extern __shared__ uint8_t smem_raw[];
     uint8_t* smem = (uint8_t*)(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
@@ -646,7 +659,7 @@ __global__ __launch_bounds__(GEMM_THREADS, 1) void gemm_tcgen05_persistent_kerne
     __shared__ uint32_t tmem_slot_p;
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int kb_total = (p.K + BK - 1) / BK;
-    const int total_tiles = m_tiles * n_tiles;
+    int total_tiles = m_tiles * n_tiles;
     const uint32_t full0 = smem_u32(bars), empty0 = smem_u32(bars + PSTAGES);
     const uint32_t accf0 = smem_u32(bars + 2 * PSTAGES), acce0 = smem_u32(bars + 2 * PSTAGES + 2);
     if (threadIdx.x == 0) {
@@ -662,7 +675,8 @@ __global__ __launch_bounds__(GEMM_THREADS, 1) void gemm_tcgen05_persistent_kerne
     const uint32_t tmem_base = tmem_slot_p;
     // The weights (the B operand) are written by no kernel: the first stages of this CTA's first tile
     // ask for their weight blocks before waiting for the kernel in front.
-    const int n_pre = (int)blockIdx.x < total_tiles ? (kb_total < PSTAGES ? kb_total : PSTAGES) : 0;
+    // (Not when grouped: which matrix a tile needs is not known before the segments are.)
+    const int n_pre = (!GROUPED && (int)blockIdx.x < total_tiles) ? (kb_total < PSTAGES ? kb_total : PSTAGES) : 0;
     if (warp == 0 && lane == 0) {
         const int b0 = ((int)blockIdx.x / m_tiles) * PBN;
         for (int i = 0; i < n_pre; ++i) {
@@ -671,13 +685,33 @@ __global__ __launch_bounds__(GEMM_THREADS, 1) void gemm_tcgen05_persistent_kerne
         }
     }
     pdl_wait();
+    if (GROUPED) {
+        for (int e = threadIdx.x; e < p.n_seg; e += GEMM_THREADS) s_first[e + 1] = (p.seg[e + 1] - p.seg[e] + BM - 1) / BM;
+        __syncthreads();
+        if (threadIdx.x == 0) {
+            int at = 0;
+            for (int e = 0; e < p.n_seg; ++e) { const int c = s_first[e + 1]; s_first[e] = at; at += c; }
+            s_first[p.n_seg] = at;
+        }
+        __syncthreads();
+        for (int e = threadIdx.x; e < p.n_seg; e += GEMM_THREADS) {
+            const int lo = p.seg[e], hi = p.seg[e + 1];
+            int j = s_first[e];
+            for (int r = lo; r < hi && j < GROUP_MAX_TILES; r += BM, ++j) { s_tab[3 * j] = r; s_tab[3 * j + 1] = hi; s_tab[3 * j + 2] = e; }
+        }
+        __syncthreads();
+        m_tiles = min(s_first[p.n_seg], GROUP_MAX_TILES);
+        total_tiles = m_tiles * n_tiles;
+    }
 
     if (warp == 0) {
         if (lane == 0) {
             int it = 0;
             bool ok = true;
             for (int tile = blockIdx.x; tile < total_tiles && ok; tile += gridDim.x) {
-                const int a0 = (tile % m_tiles) * BM, b0 = (tile / m_tiles) * PBN;
+                const int mi = tile % m_tiles;
+                const int a0 = GROUPED ? s_tab[3 * mi] : mi * BM;
+                const int b0 = (tile / m_tiles) * PBN + (GROUPED ? s_tab[3 * mi + 2] * p.b_rows : 0);
                 for (int kb = 0; kb < kb_total; ++kb, ++it) {
                     const int s = it % PSTAGES;
                     const uint32_t sa = smem_u32(smem + s * L::STAGE_BYTES);
@@ -721,8 +755,10 @@ __global__ __launch_bounds__(GEMM_THREADS, 1) void gemm_tcgen05_persistent_kerne
         int n = 0;
         for (int tile = blockIdx.x; tile < total_tiles; tile += gridDim.x, ++n) {
             const int buf = n & 1;
-            const int a0 = (tile % m_tiles) * BM, b0 = (tile / m_tiles) * PBN;
+            const int mi = tile % m_tiles;
+            const int a0 = GROUPED ? s_tab[3 * mi] : mi * BM, b0 = (tile / m_tiles) * PBN;
             const int a_row = a0 + quad * 32 + lane;
+            const bool row_on = !GROUPED || a_row < s_tab[3 * mi + 1];       // grouped: rows of the tile's own segment only
             const float row_scale = (AIRUN_FOLD_NORM && p.ssq_in && a_row < p.a_rows) ? token_scale(p, a_row) : 1.0f;   // while the MMAs run
             float ssq_acc = 0.0f;
             if (!mbar_wait(accf0 + 8 * buf, (n >> 1) & 1)) { atomicOr(p.err, AIRUN_DEV_TIMEOUT); break; }
@@ -743,6 +779,7 @@ __global__ __launch_bounds__(GEMM_THREADS, 1) void gemm_tcgen05_persistent_kerne
 #pragma unroll
                     for (int i = 0; i < 16; ++i) { v[i] *= row_scale; if (STEP == 32) u[i] *= row_scale; }
                 }
+                if (!row_on) continue;
                 if (EPI == EPI_SWIGLU) store_swiglu_normal(p, v, u, a_row, b0, c);
                 else if (EPI == EPI_RESID) ssq_acc += store_resid_normal(p, v, a_row, b0 + c);
                 else store_chunk<EPI, false>(p, v, a_row, b0, c);
@@ -853,13 +890,13 @@ int launch(const CUtensorMap& ma, const CUtensorMap& mb, const GemmParams& p, di
     return airun_launch_status();
 }
 
-template <int EPI>
+template <int EPI, bool GROUPED = false>
 int launch_persistent(const CUtensorMap& ma, const CUtensorMap& mb, const GemmParams& p, cudaStream_t stream) {
     using L = SmemLayout<PBN, PSTAGES>;
     constexpr int SMEM = L::TOTAL + 64;
     static unsigned long long configured = 0;
     static int sms_of[64];
-    auto kern = gemm_tcgen05_persistent_kernel<EPI>;
+    auto kern = gemm_tcgen05_persistent_kernel<EPI, GROUPED>;
     int dev = 0;
     cudaGetDevice(&dev);
     if (dev < 0 || dev >= 64) return AIRUN_ERR_ARG;
@@ -869,7 +906,8 @@ int launch_persistent(const CUtensorMap& ma, const CUtensorMap& mb, const GemmPa
         cudaDeviceGetAttribute(&sms_of[dev], cudaDevAttrMultiProcessorCount, dev);
     }
     const int n_sm = sms_of[dev];
-    const int m_tiles = (p.a_rows + BM - 1) / BM, n_tiles = (p.b_rows + PBN - 1) / PBN;
+    const int m_tiles = (p.a_rows + BM - 1) / BM + (GROUPED ? p.n_seg : 0), n_tiles = (p.b_rows + PBN - 1) / PBN;
+    if (GROUPED && (m_tiles > GROUP_MAX_TILES || p.n_seg > GROUP_MAX_SEGS)) return AIRUN_ERR_ARG;
     const int total = m_tiles * n_tiles;
     const int grid = total < n_sm ? total : n_sm;
     airun_launch(kern, dim3(grid), dim3(GEMM_THREADS), SMEM, stream, ma, mb, p, m_tiles, n_tiles);
@@ -1030,6 +1068,37 @@ static int gemm_launch(const void* x, const void* W, void* out, int M, int N, in
 #if AIRUN_FOLD_NORM
     if (epi == EPI_RESID) return dispatch<EPI_RESID>(swap != 0, bn, ma, mb, p, grid, stream);
 #endif
+    return AIRUN_ERR_UNSUPPORTED;
+}
+
+// The grouped product: rows seg[e] .. seg[e + 1] - 1 of x [M][K] times W[e] ([n_seg][N][K], contiguous) into the same
+// rows of out.  epi 0: float32 [M][N]; 1: bfloat16 [M][N]; 2: SwiGLU over interleaved gate/up rows, bfloat16 [M][N/2].
+// ``seg`` (int32 [n_seg + 1]) lives on the device; rows from seg[n_seg] on are left as they are.
+AIRUN_EXPORT int airun_gemm_tcgen05_grouped(const void* x, const void* W, void* out, int M, int N, int K, long long ldx,
+                                            long long ldc, int epi, const int32_t* seg, int n_seg, int* err,
+                                            cudaStream_t stream) {
+    if (M <= 0 || N <= 0 || K <= 0 || !err || !seg || n_seg <= 0) return M == 0 ? AIRUN_OK : AIRUN_ERR_ARG;
+    if (K % 8 != 0 || ldx % 8 != 0 || ((uintptr_t)x & 15) || ((uintptr_t)W & 15)) return AIRUN_ERR_ARG;
+    if (epi == EPI_SWIGLU && (N % 32 != 0)) return AIRUN_ERR_ARG;
+    if ((long long)n_seg * N > 0x7fffffffLL) return AIRUN_ERR_ARG;
+    GemmParams p = {};
+    p.a_rows = M;
+    p.b_rows = N;
+    p.K = K;
+    p.k_blocks_per_split = (K + BK - 1) / BK;
+    p.ksplit = 1;
+    p.out = out;
+    p.ldc = ldc;
+    p.err = err;
+    p.seg = seg;
+    p.n_seg = n_seg;
+    CUtensorMap ma, mb;
+    int r;
+    if ((r = make_map(&ma, x, M, K, ldx, BM)) != AIRUN_OK) return r;
+    if ((r = make_map(&mb, W, (long long)n_seg * N, K, K, PBN)) != AIRUN_OK) return r;
+    if (epi == EPI_F32) return launch_persistent<EPI_F32, true>(ma, mb, p, stream);
+    if (epi == EPI_BF16) return launch_persistent<EPI_BF16, true>(ma, mb, p, stream);
+    if (epi == EPI_SWIGLU) return launch_persistent<EPI_SWIGLU, true>(ma, mb, p, stream);
     return AIRUN_ERR_UNSUPPORTED;
 }
 

@@ -210,6 +210,38 @@ def linear_swiglu_bf16(ctx, x: torch.Tensor, w_gu: torch.Tensor, out: torch.Tens
     return True
 
 
+GROUPED_MAX_TILES = 1024
+
+
+def grouped_linear_bf16(ctx, x: torch.Tensor, w: torch.Tensor, out: torch.Tensor, seg: torch.Tensor, swiglu_group: int = 0) -> bool:
+    """Rows seg[e] .. seg[e+1]-1 of x [M, K] times w[e]^T (w [E, N, K]) on tcgen05, the segments read from the device.
+    ``swiglu_group`` 16: the rows of w[e] alternate between blocks of 16 gate and 16 up rows and out is the gated
+    unit's result, bfloat16 [M, N/2]; 0: out [M, N] float32 or bfloat16.  False when the kernel does not take the
+    sizes (the caller then uses the plain grouped product)."""
+    M, K = x.shape
+    E, N = w.shape[0], w.shape[1]
+    if ("gemm" in DISABLED or x.dtype != torch.bfloat16 or w.dtype != torch.bfloat16 or M == 0 or K % 8 or not x.is_contiguous()
+            or not w.is_contiguous() or x.data_ptr() % 16 or w.data_ptr() % 16 or (M + 127) // 128 + E > GROUPED_MAX_TILES):
+        return False
+    if swiglu_group:
+        if swiglu_group != 16 or N % 32 or out.dtype != torch.bfloat16 or tuple(out.shape) != (M, N // 2):
+            return False
+        epi = EPI_SWIGLU
+    else:
+        if out.dtype not in (torch.float32, torch.bfloat16) or tuple(out.shape) != (M, N):
+            return False
+        epi = EPI_F32 if out.dtype == torch.float32 else EPI_BF16
+    _cuda(x, w, out, seg)
+    _need(out.stride(1) == 1 and seg.dtype == torch.int32 and seg.numel() >= E + 1 and seg.is_contiguous(),
+          "out must be row-major and seg int32 [E + 1]")
+    f = _fn("gemm_tcgen05", "airun_gemm_tcgen05_grouped",
+            [c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_longlong, c_longlong, c_int, c_void_p, c_int, c_void_p, c_void_p])
+    _check(f(_p(x), _p(w), _p(out), M, N, K, x.stride(0) if M > 1 else max(K, x.stride(0)),
+             out.stride(0) if M > 1 else max(out.shape[1], out.stride(0)), epi, _p(seg), E, _p(ctx.err), _stream()),
+           "gemm_tcgen05_grouped")
+    return True
+
+
 # Folding the residual add and the RMSNorm into the products around them (EPI_RESID + token scales)
 # removes two launches per layer, but as measured on the Qwen3-8B shape the heavier epilogues cost
 # what the launches saved (decode) or more (prompt portions, whose epilogue accesses are strided),

@@ -77,10 +77,15 @@ class RoutedExperts(FeedForward):
         ops.moe_route(h, self.w_router, top, self.softmax, self.renorm, ctx.req_of_token, ids, wts, rank, self.counts, seg)
         xs = ws.alloc((M, self.H), self.dtype)
         ops.moe_scatter(h, top, ids, wts, rank, seg, self.on_input, xs, row_of)
-        gu = ws.alloc((M, 2 * self.I), torch.float32)
-        grouped_linear(ctx, xs, self.w_gu, gu, seg)
         act = ws.alloc((M, self.I), self.dtype)
-        ops.swiglu(gu, act, self.group)
+        fused = False
+        if xs.dtype == torch.bfloat16:
+            from ..kernels import fast
+            fused = fast.grouped_linear_bf16(ctx, xs, self.w_gu, act, seg, swiglu_group=self.group)
+        if not fused:
+            gu = ws.alloc((M, 2 * self.I), torch.float32)
+            grouped_linear(ctx, xs, self.w_gu, gu, seg)
+            ops.swiglu(gu, act, self.group)
         ys = ws.alloc((M, self.H), torch.float32)
         grouped_linear(ctx, act, self.w_down, ys, seg)
         delta = ws.alloc((T, self.H), torch.float32)
@@ -89,7 +94,12 @@ class RoutedExperts(FeedForward):
 
 
 def grouped_linear(ctx, x: torch.Tensor, w: torch.Tensor, out: torch.Tensor, seg: torch.Tensor) -> None:
-    """Rows seg[e] .. seg[e+1]-1 of x times w[e]^T: x [M, K], w [E, N, K], out [M, N], seg int32 [E+1] on the device."""
+    """Rows seg[e] .. seg[e+1]-1 of x times w[e]^T: x [M, K], w [E, N, K], out [M, N], seg int32 [E+1] on the device.
+    bfloat16 operands go to the tensor-core kernel where it takes the sizes, everything else to the plain one."""
+    if x.dtype == torch.bfloat16:
+        from ..kernels import fast
+        if fast.grouped_linear_bf16(ctx, x, w, out, seg):
+            return
     ops.gemm_simt_grouped(x, w, out, seg)
 
 

@@ -773,3 +773,35 @@ def test_replay_tool_runs_a_pogarax_folder(folders, tmp_path):
     assert rp.close() == 0
     wa, wb = P.plain_forward(cfg, W, seqs[0]).numpy(), P.plain_forward(cfg, W, seqs[1]).numpy()
     assert_close(np.concatenate([a, b]), np.stack([wa[0], wa[29], wa[49], wb[22]]).astype(np.float32), "float32", "replay")
+
+
+@gpu
+@pytest.mark.parametrize("M,E,N,K", [(300, 5, 96, 64), (37, 12, 512, 128), (1500, 3, 288, 200), (64, 64, 64, 256)])
+def test_tensor_core_product_per_segment(M, E, N, K):
+    """The grouped tcgen05 product against float64: segments of every size (empty ones, one row, several tiles),
+    rows left over behind the last segment, with the plain result and with the gated unit in its epilogue."""
+    from airun_b200.kernels import fast
+    g = torch.Generator().manual_seed(M + E)
+    cuts = sorted(int(c) for c in torch.randint(0, M - 3, (E - 1,), generator=g))
+    seg_host = [0] + cuts + [M - 3]
+    if E >= 3:
+        seg_host[2] = seg_host[1]                                     # an empty segment
+    seg_host = sorted(seg_host)
+    seg = torch.tensor(seg_host, dtype=torch.int32, device="cuda")
+    x, w = torch.randn(M, K, generator=g), torch.randn(E, N, K, generator=g) / math.sqrt(K)
+    ctx = SimpleNamespace(err=torch.zeros(1, dtype=torch.int32, device="cuda"))
+    xd, wd = dev(x, torch.bfloat16), dev(w, torch.bfloat16)
+    out = torch.full((M, N), 7.0, device="cuda")
+    assert fast.grouped_linear_bf16(ctx, xd, wd, out, seg)
+    act = torch.full((M, N // 2), 7.0, device="cuda", dtype=torch.bfloat16)
+    assert fast.grouped_linear_bf16(ctx, xd, wd, act, seg, swiglu_group=16)
+    assert int(ctx.err.item()) == 0
+    xr, wr = xd.cpu().double(), wd.cpu().double()
+    for e in range(E):
+        lo, hi = seg_host[e], seg_host[e + 1]
+        want = xr[lo:hi] @ wr[e].T
+        assert torch.allclose(out[lo:hi].cpu().double(), want, atol=2e-3, rtol=2e-3), f"segment {e}"
+        gu = want.view(hi - lo, N // 32, 2, 16)
+        unit = (P.plain_silu(gu[:, :, 0]) * gu[:, :, 1]).reshape(hi - lo, N // 2)
+        assert torch.allclose(act[lo:hi].cpu().double(), unit, atol=2e-2, rtol=2e-2), f"gated unit of segment {e}"
+    assert (out[M - 3:] == 7.0).all() and (act[M - 3:] == 7.0).all()
