@@ -4,7 +4,7 @@
 //   weight = s of the chosen expert, divided by the sum of the chosen ones when `renorm`
 // The rows of a step are then sorted by expert so that every expert's rows are one segment of a buffer and a
 // grouped product (gemm_simt.cu) runs each segment against its expert's matrices:
-//   route    ids, weights, and each row's rank among its expert's rows (a counter per expert)
+//   route    from the logits: ids, weights, and each row's rank among its expert's rows (a counter per expert)
 //   offsets  seg[e] = rows of the experts before e
 //   scatter  xs[seg[e] + rank] = h[t] (times the weight, when the weight scales the expert's INPUT)
 //   ...      the experts' products on xs ...
@@ -16,30 +16,24 @@
 
 #define MOE_MAX_EXPERTS 1024
 
-template <typename TH>
+// One warp per token; z [T][E] are the router's logits (a product like any other, accumulated in float32).
 __global__ __launch_bounds__(128) void moe_route_kernel(
-    const TH* __restrict__ h, const TH* __restrict__ wr, int W, int E, int top, int softmax_scores, int renorm,
+    const float* __restrict__ z, int T, int E, int top, int softmax_scores, int renorm,
     const int32_t* __restrict__ req_of_token, int32_t* __restrict__ ids, float* __restrict__ wts, int32_t* __restrict__ rank,
     int32_t* __restrict__ counts) {
     pdl_trigger();
     pdl_wait();
-    __shared__ float s_score[MOE_MAX_EXPERTS];
-    const int t = blockIdx.x;
+    extern __shared__ float s_all[];                     // [4][E]
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int t = blockIdx.x * 4 + warp;
+    if (t >= T) return;
+    float* s_score = s_all + (size_t)warp * E;
     if (req_of_token[t] < 0) {
-        for (int k = threadIdx.x; k < top; k += blockDim.x) ids[(size_t)t * top + k] = -1;
+        for (int k = lane; k < top; k += 32) ids[(size_t)t * top + k] = -1;
         return;
     }
-    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-    const TH* hr = h + (size_t)t * W;
-    for (int e = warp; e < E; e += 4) {
-        const TH* w = wr + (size_t)e * W;
-        float acc = 0.0f;
-        for (int c = lane; c < W; c += 32) acc = fmaf(to_f32<TH>(hr[c]), to_f32<TH>(w[c]), acc);
-        acc = warp_sum(acc);
-        if (lane == 0) s_score[e] = acc;
-    }
-    __syncthreads();
-    if (warp != 0) return;
+    for (int e = lane; e < E; e += 32) s_score[e] = z[(size_t)t * E + e];
+    __syncwarp();
     if (softmax_scores) {
         float m = -INFINITY;
         for (int e = lane; e < E; e += 32) m = fmaxf(m, s_score[e]);
@@ -127,21 +121,15 @@ __global__ __launch_bounds__(256) void moe_combine_kernel(
     }
 }
 
-AIRUN_EXPORT int airun_moe_route(const void* h, const void* wr, int dtype, int T, int W, int E, int top, int softmax_scores,
-                                 int renorm, const int32_t* req_of_token, int32_t* ids, float* wts, int32_t* rank, int32_t* counts,
+AIRUN_EXPORT int airun_moe_route(const float* z, int T, int E, int top, int softmax_scores, int renorm,
+                                 const int32_t* req_of_token, int32_t* ids, float* wts, int32_t* rank, int32_t* counts,
                                  int32_t* seg, cudaStream_t stream) {
-    if (T < 0 || W <= 0 || E <= 0 || E > MOE_MAX_EXPERTS || top <= 0 || top > E || !req_of_token || !ids || !wts || !rank ||
+    if (T < 0 || E <= 0 || E > MOE_MAX_EXPERTS || top <= 0 || top > E || !z || !req_of_token || !ids || !wts || !rank ||
         !counts || !seg)
         return AIRUN_ERR_ARG;
     if (T == 0) return AIRUN_OK;
-    if (dtype == AIRUN_DT_F32)
-        airun_launch(moe_route_kernel<float>, dim3(T), dim3(128), 0, stream, (const float*)h, (const float*)wr, W, E, top,
-                     softmax_scores, renorm, req_of_token, ids, wts, rank, counts);
-    else if (dtype == AIRUN_DT_BF16)
-        airun_launch(moe_route_kernel<__nv_bfloat16>, dim3(T), dim3(128), 0, stream, (const __nv_bfloat16*)h,
-                     (const __nv_bfloat16*)wr, W, E, top, softmax_scores, renorm, req_of_token, ids, wts, rank, counts);
-    else
-        return AIRUN_ERR_UNSUPPORTED;
+    airun_launch(moe_route_kernel, dim3(ceil_div_i(T, 4)), dim3(128), (size_t)4 * E * sizeof(float), stream, z, T, E, top,
+                 softmax_scores, renorm, req_of_token, ids, wts, rank, counts);
     airun_launch(moe_offsets_kernel, dim3(1), dim3(32), 0, stream, (const int32_t*)counts, seg, E);
     return airun_launch_status();
 }

@@ -67,7 +67,8 @@ DISABLED = set(filter(None, os.environ.get("AIRUN_DISABLE_FAST", "").split(","))
 
 def all_libraries():
     return [("gemm_tcgen05", None), ("gemm_tcgen05", {"AIRUN_FOLD_NORM": 1}), ("attention_plan", None), ("attention_mma", {"HD": 128}), ("attention_mma", {"HD": 64}),
-            ("attention_tcgen05", {"HD": 128}), ("attention_tcgen05", {"HD": 64}), ("diff_attention_mma", None)]
+            ("attention_tcgen05", {"HD": 128}), ("attention_tcgen05", {"HD": 64}), ("diff_attention_mma", None),
+            ("latent_attention_mma", None)]
 
 
 def scratch_for(device: torch.device) -> Tuple[torch.Tensor, torch.Tensor]:
@@ -623,4 +624,29 @@ def diff_attention_bf16(ctx, q, out, cache, part) -> bool:
     max_tiles = (T + DIFF_TILE_ROWS - 1) // DIFF_TILE_ROWS + int(ctx.num_reqs)
     f = _fn("diff_attention_mma", "airun_diff_attention_mma", sig + [c_int] + csig + [c_int, c_void_p, c_void_p])
     _check(f(*common, max_tiles, *consts, 1 if single else 0, _p(ctx.err), _stream()), "diff_attention_mma")
+    return True
+
+
+def latent_attention_bf16(ctx, qlat, out, cache, part) -> bool:
+    """Attention over a cached latent on the tensor cores (csrc/latent_attention_mma.cu): prompt portions with several
+    tokens a CTA, steps of single tokens with one token a CTA whose warps share the keys.  False: the caller runs the
+    plain kernel (rows that are no multiple of 8 elements, or too long for the shared memory)."""
+    H, R, rd = part.nh, part.R, part.rd
+    KD = R + rd
+    if ("latent_attention" in DISABLED or qlat.dtype != torch.bfloat16 or cache.pool.dtype != torch.bfloat16 or KD % 8
+            or KD > 640):
+        return False
+    _cuda(qlat, out, cache.pool, cache.block_table, ctx.positions, ctx.req_of_token, ctx.err, part.sink)
+    T = qlat.shape[0]
+    _need(tuple(qlat.shape) == (T, H * KD) and qlat.is_contiguous() and tuple(out.shape) == (T, H * R) and out.is_contiguous()
+          and out.dtype == torch.bfloat16, "qlat / out must be contiguous bfloat16 [T, H*(R+rd)] / [T, H*R]")
+    pool, bt = cache.pool, cache.block_table
+    _need(pool.is_contiguous() and pool[0].numel() == cache.page_size * KD, "the cache pages do not fit the latent rows")
+    _need(qlat.data_ptr() % 16 == 0 and pool.data_ptr() % 16 == 0, "qlat and the cache pages must begin on 16-byte boundaries")
+    f = _fn("latent_attention_mma", "airun_latent_attention_mma",
+            [c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int, c_int, c_int,
+             c_float, c_int, c_void_p, c_int, c_void_p, c_void_p])
+    _check(f(_p(qlat), _p(out), _p(pool), _p(bt), bt.stride(0), _p(ctx.positions), _p(ctx.req_of_token), T, int(ctx.num_reqs),
+             pool.shape[0], int(cache.page_size), H, R, rd, float(part.scale), int(part.window), _p(part.sink),
+             1 if getattr(ctx, "decode_only", False) else 0, _p(ctx.err), _stream()), "latent_attention_mma")
     return True

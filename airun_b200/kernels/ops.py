@@ -642,25 +642,22 @@ def latent_attention(qlat: torch.Tensor, out: torch.Tensor, cache, ctx, H: int, 
 
 
 # ---------------------------------------------------------------- routed experts
-def moe_route(h: torch.Tensor, w_router: torch.Tensor, top: int, softmax_scores: bool, renorm: bool, req_of_token: torch.Tensor,
+def moe_route(logits: torch.Tensor, top: int, softmax_scores: bool, renorm: bool, req_of_token: torch.Tensor,
               ids: torch.Tensor, wts: torch.Tensor, rank: torch.Tensor, counts: torch.Tensor, seg: torch.Tensor) -> None:
-    """ids / wts [T, top]: every token's ``top`` experts by score (sigmoid or softmax of h @ w_router^T, float32) and
-    their weights; rank [T, top]: the row's place among its expert's rows; seg [E + 1]: where each expert's rows begin.
-    ``counts`` (int32 [E]) must be zero on entry."""
-    _cuda(h, w_router, req_of_token, ids, wts, rank, counts, seg)
-    T, W = h.shape
-    E = w_router.shape[0]
-    _need(h.is_contiguous() and w_router.is_contiguous() and w_router.shape[1] == W and h.dtype == w_router.dtype,
-          "h [T, W] and the router [E, W] must be contiguous and of one type")
+    """ids / wts [T, top]: every token's ``top`` experts by score (sigmoid or softmax of the router's ``logits``
+    [T, E], float32) and their weights; rank [T, top]: the row's place among its expert's rows; seg [E + 1]: where each
+    expert's rows begin.  ``counts`` (int32 [E]) must be zero on entry."""
+    _cuda(logits, req_of_token, ids, wts, rank, counts, seg)
+    _need(logits.dtype == torch.float32 and logits.dim() == 2 and logits.is_contiguous(), "logits must be contiguous float32 [T, E]")
+    T, E = logits.shape
     _need(E <= 1024 and 1 <= top <= E, "1 to 1024 experts, top of them a token")
     for t_, dt in ((ids, torch.int32), (wts, torch.float32), (rank, torch.int32)):
         _need(t_.dtype == dt and t_.numel() >= T * top and t_.is_contiguous(), "ids / wts / rank must be [T, top]")
     _need(counts.dtype == torch.int32 and counts.numel() >= E and seg.dtype == torch.int32 and seg.numel() >= E + 1,
           "counts / seg must be int32 [E] / [E + 1]")
     f = _fn("moe", "airun_moe_route",
-            [c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p,
-             c_void_p, c_void_p])
-    _check(f(_p(h), _p(w_router), _dt(h), T, W, E, int(top), 1 if softmax_scores else 0, 1 if renorm else 0, _p(req_of_token),
+            [c_void_p, c_int, c_int, c_int, c_int, c_int, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p])
+    _check(f(_p(logits), T, E, int(top), 1 if softmax_scores else 0, 1 if renorm else 0, _p(req_of_token),
              _p(ids), _p(wts), _p(rank), _p(counts), _p(seg), _stream()), "moe_route")
 
 

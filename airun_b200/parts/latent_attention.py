@@ -111,18 +111,35 @@ class LatentAttention(Mixer):
         ops.latent_query(q, qn, qlat, nh, self.D, R, rd, self.rot_dims, self.inv_freq, self.rot_mult, ctx)
         head_linear(ctx, qn.view(T, nh, self.D), self.w_ukT, qlat.view(T, nh, R + rd)[:, :, :R])
         olat = ws.alloc((T, nh * R), self.dtype)
-        ops.latent_attention(qlat, olat, cache, ctx, nh, R, rd, self.scale, self.window, self.sink)
+        self.attend(ctx, qlat, olat, cache)
         attn = ws.alloc((T, nh * self.Dv), self.dtype)
         head_linear(ctx, olat.view(T, nh, R), self.w_uv, attn.view(T, nh, self.Dv))
         delta = ws.alloc((T, self.H), torch.float32)
         linear(ctx, attn, self.w_out, delta)
         return delta
 
+    def attend(self, ctx, qlat: torch.Tensor, out: torch.Tensor, cache) -> None:
+        if qlat.dtype == torch.bfloat16:
+            from ..kernels import fast
+            if fast.latent_attention_bf16(ctx, qlat, out, cache, self):
+                return
+        ops.latent_attention(qlat, out, cache, ctx, self.nh, self.R, self.rd, self.scale, self.window, self.sink)
+
 
 def head_linear(ctx, x: torch.Tensor, w: torch.Tensor, out: torch.Tensor) -> None:
     """out[:, h, :] = x[:, h, :] @ w[h]^T for every head: x [T, heads, K], w [heads, N, K], out [T, heads, N]
-    (x and out may be column slices of wider rows)."""
+    (x and out may be column slices of wider rows).  Prompt portions in bfloat16 run head by head on the tensor
+    cores where the slices are aligned for them; everything else is one launch of the plain batched product."""
+    T, heads, K = x.shape
+    if (x.dtype == torch.bfloat16 and T > HEAD_LOOP_MIN_TOKENS and K % 8 == 0 and x.stride(0) % 8 == 0
+            and (x.stride(1) * 2) % 16 == 0 and x.data_ptr() % 16 == 0):
+        from ..kernels import fast
+        if all(fast.linear_bf16(ctx, x[:, h], w[h], out[:, h]) for h in range(heads)):
+            return
     ops.gemm_simt_batched(x, w, out)
+
+
+HEAD_LOOP_MIN_TOKENS = 128
 
 
 register_part("mixer", "latent_attention", LatentAttention)

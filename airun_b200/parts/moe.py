@@ -21,6 +21,7 @@ import torch
 from ..kernels import ops
 from ..weights.loader import WeightSpec
 from .base import FeedForward, register_part
+from .linear import linear
 from .mlp import INTERLEAVE
 
 
@@ -74,7 +75,9 @@ class RoutedExperts(FeedForward):
         wts = ws.alloc((T, top), torch.float32)
         seg = ws.alloc((self.E + 1,), torch.int32)
         self.counts.zero_()
-        ops.moe_route(h, self.w_router, top, self.softmax, self.renorm, ctx.req_of_token, ids, wts, rank, self.counts, seg)
+        logits = ws.alloc((T, self.E), torch.float32)
+        linear(ctx, h, self.w_router, logits)
+        ops.moe_route(logits, top, self.softmax, self.renorm, ctx.req_of_token, ids, wts, rank, self.counts, seg)
         xs = ws.alloc((M, self.H), self.dtype)
         ops.moe_scatter(h, top, ids, wts, rank, seg, self.on_input, xs, row_of)
         act = ws.alloc((M, self.I), self.dtype)

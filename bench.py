@@ -705,6 +705,171 @@ def workload_vedizen(a) -> int:
 
 
 
+# ---------------------------------------------------------------------------------------------------------
+# The Pogarax design beside the Vedizen design at equal size (--workload pogarax)
+def pogarax_pair(size: dict):
+    """(Pogarax configuration, Vedizen configuration) with the same width, head counts, vocabulary and six layer runs a
+    token.  Pogarax: gated delta rule (heads x 64 x 128, q/k heads halved, 4 taps) with a dense feed-forward, latent
+    attention (heads x (128 + 64), values of 128, latent 512, queries through a latent of width/2, window 2,048) with 16
+    experts of half the feed-forward size of which a token uses two (the dense layer's FLOPs), the same pair again with the
+    attention on the first one's cached rows, a third delta layer, and a time mix (width/64 heads of 64) with experts.
+    Vedizen: as in its own workload (gated linear attention heads x 64 x 128, differential attention in chunks of 2,048)."""
+    from airun_b200.config import PogaraxConfig
+    W, F, H = size["width"], size["ff"], size["heads"]
+    dense = dict(kind="dense", ff=F)
+    moe = dict(kind="moe", expert=dict(ff=F // 2), router=dict(experts=16, top=2))
+    delta = dict(type="channel_delta", mixer=dict(heads=H, kv_heads=H // 2, dim=64, vdim=128, conv=4), mlp=dense)
+    lat = dict(heads=H, dim=128, rot_dim=64, vdim=128, q_rank=W // 2, kv_rank=512, scale=192 ** -0.5, mask=dict(size=2048),
+               rot=dict(dims=64, base=1e6, scaling=dict(factor=4.0, original=4096, fast=32.0, slow=1.0)))
+    layers = [delta, dict(type="latent_attention", mixer=dict(lat), mlp=moe), delta,
+              dict(type="latent_attention", mixer=dict(lat, kv_from=1), mlp=moe), delta,
+              dict(type="wkv", mixer=dict(heads=W // 64, dim=64), mlp=moe)]
+    pog = PogaraxConfig.from_dict(dict(architecture="Pogarax", vocab=VEDIZEN_VOCAB, width=W, norm=dict(eps=1e-5),
+                                       residual_mult=0.7, layers=layers))
+    return pog, vedizen_pair(size)[0]
+
+
+def workload_pogarax(a) -> int:
+    """Prefill (one 2,048-token prompt) and decode (batch 8 and 64 at a context of 1,024) of the Pogarax design and of
+    the Vedizen design at equal size, through the step function and its CUDA graphs, and how long each kind of kernel
+    runs inside the prefill step and the batch-64 decode step (CUDA events around every call of the kind, the step
+    launched kernel by kernel), with the fraction of the measured peak its bytes or FLOPs over that time come to.  One
+    JSON line per size."""
+    import torch
+    from airun_b200 import Engine, EngineOptions, StepEntry
+    from airun_b200.kernels import fast, ops
+    pk = peaks()
+    T, ctx_len, steps = 2048, 1024, max(8, min(a.steps, 32))
+    fp32_peak = 148 * 128 * 2 * 1.965e9          # FMA lanes x 2 x the highest SM clock: nominal, no measured figure
+    for name in (a.sizes.split(",") if a.sizes else list(VEDIZEN_SIZES)):
+        size = VEDIZEN_SIZES[name]
+        W, F, H, G = size["width"], size["ff"], size["heads"], size["kv_heads"]
+        line = {"workload": "pogarax", "size": size, "layer_runs": 6, "vocab": VEDIZEN_VOCAB, "dtype": "bf16",
+                "data": "synthetic, random weights", "prompt": T, "decode_context": ctx_len, "peaks": pk["source"], "models": {}}
+        for model, cfg in zip(("pogarax", "vedizen"), pogarax_pair(size)):
+            eng = Engine.from_config(cfg, seed=0, options=EngineOptions(
+                dtype="bfloat16", page_size=16, cache_tokens=64 * (ctx_len + 4 * steps + 64) + 4096, max_batch_tokens=T,
+                max_requests=64, max_context=max(T, ctx_len + 4 * steps + 64)))
+            win = lambda t: sum(min(i + 1, 2048) for i in range(t))      # keys all tokens of a t-token prompt see together
+            # kind -> (module, function, work at t tokens of one prompt or None, work at a batch of b single tokens, bound)
+            if model == "pogarax":
+                R, rd, D, Dv, qr, Fe, E, top, Hw = 512, 64, 128, 128, W // 2, F // 2, 16, 2, W // 64
+                kinds = {
+                    "norm on the output + add (rms)": (ops, "postnorm_add", lambda t: 12 * t * W * 14.0, lambda b: 12 * b * W * 14.0, "hbm"),
+                    "latent: norms, rotation, cache write": (ops, "latent_prepare", lambda t: 2 * t * ((qr + R + rd) * 4.0 + qr * 2 + (R + rd)),
+                                                             lambda b: 2 * b * ((qr + R + rd) * 4.0 + qr * 2 + (R + rd)), "hbm"),
+                    "latent: query parts and rotation": (ops, "latent_query", lambda t: 2 * t * H * ((D + rd) * 4.0 + (D + rd) * 2),
+                                                         lambda b: 2 * b * H * ((D + rd) * 4.0 + (D + rd) * 2), "hbm"),
+                    "latent attention": (ops, "latent_attention", lambda t: 2 * H * 2.0 * (2 * R + rd) * win(t),
+                                         lambda b: 2 * b * min(ctx_len, 2048) * (R + rd) * 2.0, "mixed"),
+                    "products per head (Wuk, Wuv)": (ops, "gemm_simt_batched", lambda t: 2 * t * H * 2.0 * (D * R + R * Dv),
+                                                     lambda b: 2 * H * (D * R + R * Dv) * 2.0, "tensor"),
+                    "delta rule: convolution": (ops, "short_conv", lambda t: 3 * t * (H * 64 + H * 128) * 8.0, lambda b: 3 * b * (H * 64 + H * 128) * 8.0, "hbm"),
+                    "low-rank second halves (decays, gate)": (ops, "lowrank_act", lambda t: t * (3 * (H * 64 + H * 128) + W) * 4.0,
+                                                              lambda b: b * (3 * (H * 64 + H * 128) + W) * 4.0, "hbm"),
+                    "recurrence (delta rule, time mix)": (ops, "recurrent_state", lambda t: t * (3 * H * 64 * 128 * 9.0 + Hw * 64 * 64 * 6.0),
+                                                          lambda b: b * (3 * H * 64 * 128 + Hw * 64 * 64) * 8.0, "fp32"),
+                    "norm and gate of the heads": (ops, "gla_out_gate", lambda t: t * (3 * H * 128 + W) * 10.0, lambda b: b * (3 * H * 128 + W) * 10.0, "hbm"),
+                    "token shift": (ops, "token_shift", lambda t: t * W * 14.0, lambda b: b * W * 14.0, "hbm"),
+                    "gate/up product + gated unit (dense)": (fast, "linear_swiglu_bf16", lambda t: 3 * 2.0 * t * W * 2 * F, lambda b: 3 * W * 2 * F * 2.0, "tensor"),
+                    "expert products (gate/up + unit, down)": (fast, "grouped_linear_bf16", lambda t: 3 * t * top * 6.0 * W * Fe,
+                                                               lambda b: 3 * min(E, b * top) * 3 * W * Fe * 2.0, "tensor"),
+                    "router": (ops, "moe_route", lambda t: 3 * t * W * 2.0, lambda b: 3 * (b * W + E * W) * 2.0, "hbm"),
+                    "rows to experts and back": (ops, "moe_scatter", lambda t: 3 * t * (W * 2 + top * W * 2.0), lambda b: 3 * b * (W * 2 + top * W * 2.0), "hbm"),
+                    "sum of a token's experts": (ops, "moe_combine", lambda t: 3 * t * (top + 1) * W * 4.0, lambda b: 3 * b * (top + 1) * W * 4.0, "hbm"),
+                }
+            else:
+                n_att, n_gla = 3, 3
+                kinds = {
+                    "norm (dynamic tanh)": (ops, "dyt_norm", lambda t: 7 * t * W * 14.0, lambda b: 7 * b * W * 14.0, "hbm"),
+                    "q/k/v bias + cache write": (ops, "qkv_bias_store", lambda t: n_att * t * ((H + G) * 128 + G * 128) * 6.0,
+                                                 lambda b: n_att * b * ((H + G) * 128 + G * 128) * 6.0, "hbm"),
+                    "differential attention": (fast, "diff_attention_bf16", lambda t: n_att * H * 2.0 * (2 * 64 + 2 * 128) * t * (t + 1) / 2,
+                                               lambda b: n_att * b * ctx_len * G * 256 * 2.0, "mixed"),
+                    "linear attention: decay": (ops, "gla_decay", lambda t: n_gla * t * H * 64 * 4.0, lambda b: n_gla * b * H * 64 * 4.0, "hbm"),
+                    "linear attention: recurrence": (ops, "gla_recurrent", lambda t: n_gla * t * H * 64 * 128 * 5.0,
+                                                     lambda b: n_gla * b * H * 64 * 128 * 8.0, "fp32"),
+                    "linear attention: norm and gate": (ops, "gla_out_gate", lambda t: n_gla * t * H * 128 * 10.0, lambda b: n_gla * b * H * 128 * 10.0, "hbm"),
+                    "gate/up product + gated unit": (fast, "linear_glu_clamped_bf16", lambda t: 6 * 2.0 * t * W * 2 * F, lambda b: 6 * W * 2 * F * 2.0, "tensor"),
+                }
+            res = {}
+            pre_ms = time_prefill(eng, T, runs=5)
+            b64 = time_decode_onward(eng, 64, ctx_len, steps, a.warmup, "v")
+            b8 = time_decode_onward(eng, 8, ctx_len, steps, a.warmup, "w")
+            res["prefill"] = {"ms": round(pre_ms, 3), "tokens_per_s": round(T / pre_ms * 1e3, 1)}
+            res["decode_b8"] = {"ms_per_step": round(b8, 4), "tokens_per_s": round(8 / b8 * 1e3, 1)}
+            res["decode_b64"] = {"ms_per_step": round(b64, 4), "tokens_per_s": round(64 / b64 * 1e3, 1)}
+            spans = {k: [] for k in kinds}
+            real = {k: getattr(v[0], v[1]) for k, v in kinds.items()}
+
+            def timed(kind):
+                def call(*x, **kw):
+                    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+                    e0.record()
+                    out = real[kind](*x, **kw)
+                    e1.record()
+                    spans[kind].append((e0, e1))
+                    return out
+                return call
+
+            def step_times(run):
+                best = {}
+                for _ in range(4):
+                    for k in spans:
+                        spans[k].clear()
+                    run()
+                    torch.cuda.synchronize()
+                    for k, evs in spans.items():
+                        us = sum(e0.elapsed_time(e1) for e0, e1 in evs) * 1e3
+                        best[k] = min(best.get(k, us), us)
+                return best
+
+            toks = torch.randint(0, eng.config.vocab_size, (T,), generator=torch.Generator().manual_seed(3)).tolist()
+            rids = [f"k{i}" for i in range(64)]
+            count = [0]
+
+            def run_prefill():
+                count[0] += 1
+                eng.manager.add_request(f"kp{count[0]}")
+                eng.runner.step([StepEntry(f"kp{count[0]}", toks, (T - 1,))])
+                eng.manager.free_request(f"kp{count[0]}")
+
+            def run_decode():
+                eng.runner.step([StepEntry(r, [toks[j]], (0,)) for j, r in enumerate(rids)])
+
+            graphs, eng.runner.use_graphs = eng.runner.use_graphs, False
+            for k, v in kinds.items():
+                setattr(v[0], v[1], timed(k))
+            try:
+                pre_t = step_times(run_prefill)
+                fill_contexts(eng, rids, ctx_len)
+                fill_states(eng)
+                dec_t = step_times(run_decode)
+            finally:
+                for k, v in kinds.items():
+                    setattr(v[0], v[1], real[k])
+                eng.runner.use_graphs = graphs
+            for r in rids:
+                eng.manager.free_request(r)
+            res["kernels"] = {}
+            for kind, (_, _, work_p, work_d, bound) in kinds.items():
+                pre_us, dec_us = max(pre_t[kind], 1e-3), max(dec_t[kind], 1e-3)
+                row = {"prefill_us": round(pre_us, 1), "decode_b64_us": round(dec_us, 1)}
+                if bound == "hbm":
+                    row["prefill_frac_of_hbm"] = round(work_p(T) / pre_us / 1e3 / pk["hbm_gbs"], 4)
+                elif bound == "fp32":
+                    row["prefill_frac_of_nominal_fp32"] = round(work_p(T) / pre_us * 1e6 / fp32_peak, 4)
+                else:
+                    row["prefill_frac_of_bf16_peak"] = round(work_p(T) / pre_us * 1e6 / (pk["bf16_tflops"] * 1e12), 4)
+                row["decode_b64_frac_of_hbm"] = round(work_d(64) / dec_us / 1e3 / pk["hbm_gbs"], 4)
+                res["kernels"][kind] = row
+            line["models"][model] = res
+            del eng
+            torch.cuda.empty_cache()
+        print(json.dumps(line), flush=True)
+    return 0
+
+
 def reference_arm(a) -> int:
     """The same metric on the reference's own CUDA kernels (compiled unmodified for sm_100), called
     through their C entry points in the order the reference's runtime calls them
@@ -884,12 +1049,13 @@ def main() -> int:
     ap.add_argument("--skip-points", action="store_true")
     ap.add_argument("--decode-only", action="store_true", help="time the decode step only (for profiling runs)")
     ap.add_argument("--prefill-only", action="store_true", help="time the 2,048-token prompt only (for profiling runs)")
-    ap.add_argument("--workload", default="decode", choices=("decode", "serve", "long", "ablate", "vedizen"),
+    ap.add_argument("--workload", default="decode", choices=("decode", "serve", "long", "ablate", "vedizen", "pogarax"),
                     help="decode: the headline line; serve: 128 requests continuously batched (Qwen3-1.7B shape); "
                          "long: a 32,768-token prompt, then decoding alone and as 16 forks (Qwen3-32B shape); "
                          "ablate: the decode step timed with one kind of kernel left out at a time; "
-                         "vedizen: prefill and decode of the Vedizen design beside the Qwen3 decoder at equal size")
-    ap.add_argument("--sizes", default="", help="vedizen: widths to run, comma separated (default: 2048,4096)")
+                         "vedizen: prefill and decode of the Vedizen design beside the Qwen3 decoder at equal size; "
+                         "pogarax: the same for the Pogarax design beside the Vedizen design")
+    ap.add_argument("--sizes", default="", help="vedizen / pogarax: widths to run, comma separated (default: 2048,4096)")
     ap.add_argument("--requests", type=int, default=128, help="serve: requests")
     ap.add_argument("--new-tokens", type=int, default=None, help="serve / long: tokens decoded per request")
     ap.add_argument("--budget", type=int, default=512, help="serve: tokens per step")
@@ -912,6 +1078,8 @@ def main() -> int:
         return workload_ablate(a)
     if a.workload == "vedizen":
         return workload_vedizen(a)
+    if a.workload == "pogarax":
+        return workload_pogarax(a)
 
     import torch
     from airun_b200 import Engine, EngineOptions, Qwen3Config

@@ -592,7 +592,9 @@ def test_router_sorts_rows_by_expert_and_brings_them_back(top, E, scores):
     ids, rank, row_of = (torch.full((T, top), -7, dtype=torch.int32, device="cuda") for _ in range(3))
     wts = torch.zeros(T, top, device="cuda")
     counts, seg = torch.zeros(E, dtype=torch.int32, device="cuda"), torch.zeros(E + 1, dtype=torch.int32, device="cuda")
-    ops.moe_route(dev(h), dev(wr), top, scores == "softmax", False, req.cuda(), ids, wts, rank, counts, seg)
+    logits = torch.empty(T, E, device="cuda")
+    ops.gemm_simt(dev(h), dev(wr), logits)
+    ops.moe_route(logits, top, scores == "softmax", False, req.cuda(), ids, wts, rank, counts, seg)
     z = h.double() @ wr.double().T
     s = torch.sigmoid(z) if scores == "sigmoid" else torch.softmax(z, dim=-1)
     val, idx = torch.topk(s, top, dim=-1)
@@ -805,3 +807,24 @@ def test_tensor_core_product_per_segment(M, E, N, K):
         unit = (P.plain_silu(gu[:, :, 0]) * gu[:, :, 1]).reshape(hi - lo, N // 2)
         assert torch.allclose(act[lo:hi].cpu().double(), unit, atol=2e-2, rtol=2e-2), f"gated unit of segment {e}"
     assert (out[M - 3:] == 7.0).all() and (act[M - 3:] == 7.0).all()
+
+
+@gpu
+@pytest.mark.parametrize("single", [False, True])
+@pytest.mark.parametrize("H,R,rd,page,window", [(3, 24, 16, 8, 13), (16, 64, 16, 16, 0), (5, 264, 8, 24, 40), (40, 32, 0, 8, 70), (16, 512, 64, 16, 100)])
+def test_tensor_core_latent_attention(H, R, rd, page, window, single):
+    """The mma kernel in both of its forms (several tokens a CTA; one token a CTA with the keys split over the warps)
+    against the equations, over scrambled pages: head counts below and above a row tile, more than 256 output
+    columns, windows that end inside a key tile, requests of one token beside portions."""
+    from airun_b200.kernels import fast
+    seq_lens, new_lens = [150, 9, 77, 1], [1, 9, 30, 1] if not single else [1, 1, 1, 1]
+    reqs, cache, (spans, ctx) = latent_case(seq_lens, new_lens, H, R, rd, page, torch.bfloat16, seed=H + R)
+    ctx.decode_only = single
+    sink = torch.randn(H, generator=torch.Generator().manual_seed(1))
+    ql = dev(torch.cat([reqs[r][1][a:b] for r, (a, b) in enumerate(spans)]), torch.bfloat16)
+    out = torch.zeros(ql.shape[0], H * R, device="cuda", dtype=torch.bfloat16)
+    part = SimpleNamespace(nh=H, R=R, rd=rd, scale=0.2, window=window, sink=dev(sink))
+    assert fast.latent_attention_bf16(ctx, ql, out, cache, part)
+    assert int(ctx.err.item()) == 0
+    want = torch.cat([plain_latent_rows(*reqs[r], H, R, rd, 0.2, window, sink, P.to_bf16_and_back)[a:b] for r, (a, b) in enumerate(spans)])
+    assert torch.allclose(out.cpu().double(), want, atol=3e-2, rtol=3e-2)
