@@ -7,15 +7,14 @@
 // them, and keeps 256 of the R output columns in registers (blockIdx.z picks the columns; the scores are computed
 // again for every 256 columns, which is cheaper than a second trip of the probabilities through shared memory).
 //
-//   RW = 4 (prompt portions): 4 warps = 4 row tiles, key tiles of 32 rows, every warp takes all keys of a tile;
-//   RW = 1 (single tokens):   one row tile, key tiles of 64 rows of which each of the 4 warps takes 16; the warps'
-//                             (maximum, sum, output) are merged through shared memory at the end, in warp order.
-// Key tiles arrive by cp.async in two stages (the next tile is on its way while this one is used); a cached row
-// is found through the request's block table.  A group of TOK batch rows that straddles two requests is handled
+//   prompt portions: 8 (or 4) warps = as many row tiles, key tiles of 32 rows, every warp takes all keys of a tile,
+//                    tiles arrive by cp.async in two stages (the next one is on its way while this one is used);
+//   single tokens:   one row tile, key tiles of 128 rows of which each of the 8 warps takes 16, one stage; the warps'
+//                    (maximum, sum, output) are merged through shared memory at the end, in warp order.
+// A cached row is found through the request's block table.  A group of TOK batch rows that straddles two requests is handled
 // request by request.  Every row keeps its own maximum and sum, so a token's result does not depend on the batch.
 #include "common.cuh"
 
-#define LM_THREADS 128
 #define LM_CW 256                 // output columns of a CTA
 #define LM_NT (LM_CW / 8)
 
@@ -51,19 +50,19 @@ struct LatentMmaArgs {
     int* err;
 };
 
-template <int RW>
-__global__ __launch_bounds__(LM_THREADS, 1) void latent_attention_mma_kernel(LatentMmaArgs a) {
+template <int RW, int KW, int STAGES>
+__global__ __launch_bounds__(32 * RW * KW, 1) void latent_attention_mma_kernel(LatentMmaArgs a) {
     pdl_trigger();
     pdl_wait();
-    constexpr int KW = 4 / RW;                 // warps that share a key tile's rows
-    constexpr int BN = RW == 4 ? 32 : 64;      // cached rows of a tile
-    constexpr int WK = BN / KW;                // cached rows of a tile one warp takes
+    constexpr int NWARP = RW * KW, NTHREAD = 32 * NWARP;
+    constexpr int BN = KW == 1 ? 32 : 16 * KW;   // cached rows of a tile
+    constexpr int WK = BN / KW;                  // cached rows of a tile one warp takes
     constexpr int ROWS = 16 * RW;
     extern __shared__ __align__(16) uint8_t lm_smem[];
     __nv_bfloat16* s_q = reinterpret_cast<__nv_bfloat16*>(lm_smem);                  // [ROWS][kdp]
     __nv_bfloat16* s_k = s_q + (size_t)ROWS * a.kdp;                                 // [2][BN][kdp]
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-    const int rw = RW == 4 ? warp : 0, kw = RW == 4 ? 0 : warp;
+    const int rw = KW == 1 ? warp : 0, kw = KW == 1 ? 0 : warp;
     const int KD = a.R + a.rd, kdp = a.kdp;
     const int t0 = blockIdx.x * a.tok, t1 = min(t0 + a.tok, a.T);
     const int h0 = blockIdx.y * a.hg, c0 = blockIdx.z * LM_CW;
@@ -86,33 +85,37 @@ __global__ __launch_bounds__(LM_THREADS, 1) void latent_attention_mma_kernel(Lat
         const int32_t* bt = a.block_table + (size_t)req * a.max_blocks;
         __syncthreads();                         // the pass before is done with the shared memory
         // the queries: row r = (token r / hg, head h0 + r % hg); rows beyond the group and the padding are zero
-        for (int e = threadIdx.x; e < ROWS * (kdp / 8); e += LM_THREADS) {
-            const int r = e / (kdp / 8), ch = e - r * (kdp / 8);
+        for (int r = warp; r < ROWS; r += NWARP) {            // a warp a row: what the row needs is worked out once
             const int tl = r / a.hg, h = h0 + r - tl * a.hg;
-            uint4 v = make_uint4(0, 0, 0, 0);
-            if (tl < n_tok && h < a.H && ch < chunks)
-                v = *reinterpret_cast<const uint4*>(a.qlat + ((size_t)(tb + tl) * a.H + h) * KD + ch * 8);
-            *reinterpret_cast<uint4*>(s_q + (size_t)r * kdp + ch * 8) = v;
+            const bool on = tl < n_tok && h < a.H;
+            const __nv_bfloat16* src = a.qlat + ((size_t)(tb + (on ? tl : 0)) * a.H + (on ? h : 0)) * KD;
+            for (int ch = lane; ch < kdp / 8; ch += 32) {
+                uint4 v = make_uint4(0, 0, 0, 0);
+                if (on && ch < chunks) v = *reinterpret_cast<const uint4*>(src + ch * 8);
+                *reinterpret_cast<uint4*>(s_q + (size_t)r * kdp + ch * 8) = v;
+            }
         }
         bool bad = false;
         auto load_tile = [&](int tile, int buf) {
             __nv_bfloat16* dst = s_k + (size_t)buf * BN * kdp;
-            for (int e = threadIdx.x; e < BN * (kdp / 8); e += LM_THREADS) {
-                const int kr = e / (kdp / 8), ch = e - kr * (kdp / 8);
+            for (int kr = warp; kr < BN; kr += NWARP) {        // a warp a cached row: one page lookup for the whole row
                 const int j = tile * BN + kr;
                 const int blk = j / a.page_size;
                 int page = -1;
-                if (ch < chunks && j <= p_last && j >= j_lo && blk < a.max_blocks) {
+                if (j <= p_last && j >= j_lo && blk < a.max_blocks) {
                     page = bt[blk];
                     if (page >= a.num_pages) { bad = true; page = -1; }
                 }
-                __nv_bfloat16* d = dst + (size_t)kr * kdp + ch * 8;
-                if (page >= 0) lm_cp16(d, a.pool + ((size_t)page * a.page_size + (j - blk * a.page_size)) * KD + ch * 8);
-                else *reinterpret_cast<uint4*>(d) = make_uint4(0, 0, 0, 0);
+                const __nv_bfloat16* src = a.pool + ((size_t)(page < 0 ? 0 : page) * a.page_size + (j - blk * a.page_size)) * KD;
+                __nv_bfloat16* d = dst + (size_t)kr * kdp;
+                for (int ch = lane; ch < kdp / 8; ch += 32) {
+                    if (page >= 0 && ch < chunks) lm_cp16(d + ch * 8, src + ch * 8);
+                    else *reinterpret_cast<uint4*>(d + ch * 8) = make_uint4(0, 0, 0, 0);
+                }
             }
             asm volatile("cp.async.commit_group;" ::: "memory");
         };
-        load_tile(tile0, 0);
+        if (STAGES == 2) load_tile(tile0, 0);
 
         float o[LM_NT][4];
 #pragma unroll
@@ -128,11 +131,12 @@ __global__ __launch_bounds__(LM_THREADS, 1) void latent_attention_mma_kernel(Lat
         const int n_pairs = min(LM_NT / 2, (a.R - c0 + 15) / 16);      // pairs of 8 output columns this CTA has
 
         for (int tile = tile0, it = 0; tile < tile_end; ++tile, ++it) {
-            const int buf = it & 1;
-            if (tile + 1 < tile_end) {
+            const int buf = STAGES == 2 ? (it & 1) : 0;
+            if (STAGES == 2 && tile + 1 < tile_end) {
                 load_tile(tile + 1, buf ^ 1);
                 asm volatile("cp.async.wait_group 1;" ::: "memory");
             } else {
+                if (STAGES == 1) load_tile(tile, 0);       // one stage: the warps of a tile wait for it together
                 asm volatile("cp.async.wait_group 0;" ::: "memory");
             }
             __syncthreads();
@@ -143,6 +147,7 @@ __global__ __launch_bounds__(LM_THREADS, 1) void latent_attention_mma_kernel(Lat
             for (int i = 0; i < WK / 8; ++i) s[i][0] = s[i][1] = s[i][2] = s[i][3] = 0.0f;
             const __nv_bfloat16* qrow = s_q + (size_t)(rw * 16 + (lane & 15)) * kdp + (lane >> 4) * 8;
             const __nv_bfloat16* krow = kt + (size_t)((lane & 7) + ((lane >> 4) << 3)) * kdp + ((lane >> 3) & 1) * 8;
+#pragma unroll 4
             for (int k0 = 0; k0 < a.kd16; k0 += 16) {
                 uint32_t af[4];
                 lm_ldsm4(af, qrow + k0);
@@ -216,9 +221,9 @@ __global__ __launch_bounds__(LM_THREADS, 1) void latent_attention_mma_kernel(Lat
 
         if (KW > 1) {
             // merge the warps' partial results of the same 16 rows, in warp order, through shared memory
-            float* s_m = reinterpret_cast<float*>(s_k);                 // [4][16] maxima, [4][16] sums, then [4][16][LM_CW]
-            float* s_l = s_m + 64;
-            float* s_o = s_l + 64;
+            float* s_m = reinterpret_cast<float*>(s_k);                 // [KW][16] maxima, [KW][16] sums, then [KW][16][LM_CW]
+            float* s_l = s_m + KW * 16;
+            float* s_o = s_l + KW * 16;
             if (qd == 0) {
                 s_m[warp * 16 + g] = m_run[0]; s_m[warp * 16 + g + 8] = m_run[1];
                 s_l[warp * 16 + g] = l_run[0]; s_l[warp * 16 + g + 8] = l_run[1];
@@ -237,10 +242,10 @@ __global__ __launch_bounds__(LM_THREADS, 1) void latent_attention_mma_kernel(Lat
                 float gm = a.sink ? a.sink[h] * 1.4426950408889634f : -INFINITY;
                 const float sk = gm;
 #pragma unroll
-                for (int w = 0; w < 4; ++w) gm = fmaxf(gm, s_m[w * 16 + r]);
-                float wgt[4], gl = a.sink ? exp2f(sk - gm) : 0.0f;
+                for (int w = 0; w < KW; ++w) gm = fmaxf(gm, s_m[w * 16 + r]);
+                float wgt[KW], gl = a.sink ? exp2f(sk - gm) : 0.0f;
 #pragma unroll
-                for (int w = 0; w < 4; ++w) {
+                for (int w = 0; w < KW; ++w) {
                     wgt[w] = s_m[w * 16 + r] == -INFINITY ? 0.0f : exp2f(s_m[w * 16 + r] - gm);
                     gl += s_l[w * 16 + r] * wgt[w];
                 }
@@ -249,7 +254,7 @@ __global__ __launch_bounds__(LM_THREADS, 1) void latent_attention_mma_kernel(Lat
                 for (int c = cs; c < LM_CW && c0 + c < a.R; c += 8) {
                     float v = 0.0f;
 #pragma unroll
-                    for (int w = 0; w < 4; ++w) v = fmaf(s_o[((size_t)w * 16 + r) * LM_CW + c], wgt[w], v);
+                    for (int w = 0; w < KW; ++w) v = fmaf(s_o[((size_t)w * 16 + r) * LM_CW + c], wgt[w], v);
                     dst[c0 + c] = __float2bfloat16_rn(v * inv);
                 }
             }
@@ -299,28 +304,31 @@ AIRUN_EXPORT int airun_latent_attention_mma(const void* qlat, void* out, const v
     a.sink = sink; a.err = err;
     a.kd16 = (KD + 15) / 16 * 16;
     a.kdp = a.kd16 + 8;
-    const int rows = single ? 16 : 64;
+    // prompt portions: 8 row tiles (128 rows) a CTA when its queries and two key tiles fit the shared memory, else 4;
+    // single tokens: one row tile, 8 warps on the 128 cached rows of a tile, one stage
+    const size_t limit = 227 * 1024;
+    int rw = single ? 1 : 8;
+    if (!single && ((size_t)128 + 2 * 32) * a.kdp * 2 > limit) rw = 4;
+    const int rows = 16 * rw, bn = single ? 128 : 32, stages = single ? 1 : 2;
     a.hg = H < rows ? H : rows;
     a.tok = rows / a.hg;
-    const int bn = single ? 64 : 32;
-    size_t smem = ((size_t)rows + 2 * bn) * a.kdp * 2;
-    if (single) { const size_t merge = (128 + (size_t)4 * 16 * LM_CW) * 4; if ((size_t)2 * bn * a.kdp * 2 < merge) smem = (size_t)rows * a.kdp * 2 + merge; }
-    if (smem > 220 * 1024) return AIRUN_ERR_ARG;
+    size_t kbytes = (size_t)stages * bn * a.kdp * 2;
+    if (single) { const size_t merge = (2 * 8 * 16 + (size_t)8 * 16 * LM_CW) * 4; if (kbytes < merge) kbytes = merge; }
+    const size_t smem = (size_t)rows * a.kdp * 2 + kbytes;
+    if (smem > limit) return AIRUN_ERR_ARG;
     dim3 grid(ceil_div_i(T, a.tok), ceil_div_i(H, a.hg), ceil_div_i(R, LM_CW));
     if (grid.y > 65535 || grid.z > 65535) return AIRUN_ERR_ARG;
-    static unsigned long long conf1 = 0, conf4 = 0;
-    if (single) {
-        if (first_on_device(conf1)) {
-            cudaError_t e = cudaFuncSetAttribute(latent_attention_mma_kernel<1>, cudaFuncAttributeMaxDynamicSharedMemorySize, 220 * 1024);
-            if (e != cudaSuccess) return (int)e;
-        }
-        airun_launch(latent_attention_mma_kernel<1>, grid, dim3(LM_THREADS), smem, stream, a);
-    } else {
-        if (first_on_device(conf4)) {
-            cudaError_t e = cudaFuncSetAttribute(latent_attention_mma_kernel<4>, cudaFuncAttributeMaxDynamicSharedMemorySize, 220 * 1024);
-            if (e != cudaSuccess) return (int)e;
-        }
-        airun_launch(latent_attention_mma_kernel<4>, grid, dim3(LM_THREADS), smem, stream, a);
-    }
+    static unsigned long long conf1 = 0, conf4 = 0, conf8 = 0;
+#define LM_LAUNCH(RW_, KW_, ST_, CONF) do { \
+        auto kern = latent_attention_mma_kernel<RW_, KW_, ST_>; \
+        if (first_on_device(CONF)) { \
+            cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)limit); \
+            if (e != cudaSuccess) return (int)e; \
+        } \
+        airun_launch(kern, grid, dim3(32 * RW_ * KW_), smem, stream, a); } while (0)
+    if (single) LM_LAUNCH(1, 8, 1, conf1);
+    else if (rw == 8) LM_LAUNCH(8, 1, 2, conf8);
+    else LM_LAUNCH(4, 1, 2, conf4);
+#undef LM_LAUNCH
     return airun_launch_status();
 }

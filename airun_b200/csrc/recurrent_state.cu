@@ -124,7 +124,7 @@ AIRUN_EXPORT int airun_token_shift(const float* x, const float* mu, int n_mix, c
 // over key channels are NS multiply-adds in a thread and two shuffles, and nothing but the state chains one token
 // to the next.  The key channels of a lane are every fourth group of four, so the four lanes of a column read
 // neighbouring float4 of the token's q, k and decay from shared memory.  Tokens are staged through shared memory
-// RS_TT at a time.  The block (request, 0, 0) also moves the request's small state on: the last inputs of the
+// a few at a time by asynchronous copies into one of two stages.  The block (request, 0, 0) also moves the request's small state on: the last inputs of the
 // short convolution (delta rule) or the last token's x (time mix).
 #define RS_DG 4
 #define RS_COLS 32
@@ -146,14 +146,22 @@ struct RecurrentArgs {
     int* err;
 };
 
+__device__ __forceinline__ void rs_cp4(float* smem, const float* gmem) {
+    asm volatile("cp.async.ca.shared.global [%0], [%1], 4;" ::"r"((uint32_t)__cvta_generic_to_shared(smem)), "l"(gmem) : "memory");
+}
+__device__ __forceinline__ void rs_cp16(float* smem, const float* gmem) {
+    asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"((uint32_t)__cvta_generic_to_shared(smem)), "l"(gmem) : "memory");
+}
+
 template <int MODE, int NS>
 __global__ __launch_bounds__(128) void recurrent_state_kernel(RecurrentArgs a) {
     pdl_trigger();
     pdl_wait();
     constexpr int DP = NS * RS_DG;
-    constexpr int TT = NS >= 64 ? RS_TT / 2 : RS_TT;          // static shared memory stays under 48 KB
-    __shared__ __align__(16) float s_q[TT][DP], s_k[TT][DP], s_g[TT][DP];
-    __shared__ float s_v[TT][RS_COLS], s_b[TT];
+    constexpr int TT = NS >= 64 ? 4 : NS >= 32 ? 8 : RS_TT;      // tokens of a stage (static shared memory stays under 48 KB)
+    // two stages: the next tokens arrive by asynchronous copies while these are used
+    __shared__ __align__(16) float s_q[2][TT][DP], s_k[2][TT][DP], s_g[2][TT][DP], s_v[2][TT][RS_COLS];
+    __shared__ float s_b[2][TT];
     const int r = blockIdx.x, head = blockIdx.y, col0 = blockIdx.z * RS_COLS;
     const int t0 = a.cu_tokens[r], n = a.cu_tokens[r + 1] - t0;
     if (n <= 0) return;
@@ -164,9 +172,58 @@ __global__ __launch_bounds__(128) void recurrent_state_kernel(RecurrentArgs a) {
     }
     const int D = a.D, Dv = a.Dv;
     const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
-    const int dg = lane & (RS_DG - 1), col = col0 + warp * (32 / RS_DG) + (lane >> 2);
+    const int dg = lane & (RS_DG - 1), cl = warp * (32 / RS_DG) + (lane >> 2), col = col0 + cl;
     const bool col_ok = col < Dv;
     const int qk_head = head / a.kv_rep;
+    // the padding beyond D and Dv is zero in both stages and is never copied into
+    for (int e = threadIdx.x; e < 2 * TT * DP; e += 128) { (&s_q[0][0][0])[e] = 0.0f; (&s_k[0][0][0])[e] = 0.0f; (&s_g[0][0][0])[e] = 0.0f; }
+    for (int e = threadIdx.x; e < 2 * TT * RS_COLS; e += 128) (&s_v[0][0][0])[e] = 0.0f;
+    __syncthreads();
+    const float* qh = a.q + (size_t)qk_head * D;
+    const float* kh = a.k + (size_t)qk_head * D;
+    const float* gh = a.g + (size_t)head * D;
+    const float* vh = a.v + (size_t)head * Dv + col0;
+    const int ncol = min(RS_COLS, Dv - col0);
+    const bool vec = (D % 4 == 0) && ((a.q_stride | a.k_stride | a.g_stride) % 4 == 0) &&
+                     ((((uintptr_t)qh | (uintptr_t)kh | (uintptr_t)gh) & 15) == 0);
+    const bool vvec = (ncol % 4 == 0) && (a.v_stride % 4 == 0) && (((uintptr_t)vh & 15) == 0);
+    auto stage = [&](int base, int buf) {
+        const int nt = min(TT, n - base);
+        if (vec) {
+            const int per = D / 4;
+            for (int e = threadIdx.x; e < nt * per; e += 128) {
+                const int tt = e / per, d = (e - tt * per) * 4;
+                const size_t row = (size_t)(t0 + base + tt);
+                rs_cp16(&s_q[buf][tt][d], qh + row * a.q_stride + d);
+                rs_cp16(&s_k[buf][tt][d], kh + row * a.k_stride + d);
+                rs_cp16(&s_g[buf][tt][d], gh + row * a.g_stride + d);
+            }
+        } else {
+            for (int e = threadIdx.x; e < nt * D; e += 128) {
+                const int tt = e / D, d = e - tt * D;
+                const size_t row = (size_t)(t0 + base + tt);
+                rs_cp4(&s_q[buf][tt][d], qh + row * a.q_stride + d);
+                rs_cp4(&s_k[buf][tt][d], kh + row * a.k_stride + d);
+                rs_cp4(&s_g[buf][tt][d], gh + row * a.g_stride + d);
+            }
+        }
+        if (vvec) {
+            const int per = ncol / 4;
+            for (int e = threadIdx.x; e < nt * per; e += 128) {
+                const int tt = e / per, c = (e - tt * per) * 4;
+                rs_cp16(&s_v[buf][tt][c], vh + (size_t)(t0 + base + tt) * a.v_stride + c);
+            }
+        } else {
+            for (int e = threadIdx.x; e < nt * ncol; e += 128) {
+                const int tt = e / ncol, c = e - tt * ncol;
+                rs_cp4(&s_v[buf][tt][c], vh + (size_t)(t0 + base + tt) * a.v_stride + c);
+            }
+        }
+        if (MODE == RS_DELTA && threadIdx.x < nt)
+            rs_cp4(&s_b[buf][threadIdx.x], a.beta + (size_t)(t0 + base + threadIdx.x) * a.beta_stride + head);
+        asm volatile("cp.async.commit_group;" ::: "memory");
+    };
+    stage(0, 0);
     float* sbase = a.state + (size_t)slot * a.slot_stride + (size_t)head * D * Dv + (col_ok ? col : 0);
     // channel of register i: group of four (i / 4) * DG + dg, element i % 4
     float S[NS], bonus[MODE == RS_WKV ? NS : 1];
@@ -176,86 +233,85 @@ __global__ __launch_bounds__(128) void recurrent_state_kernel(RecurrentArgs a) {
         S[i] = (col_ok && d < D) ? sbase[(size_t)d * Dv] : 0.0f;
         if (MODE == RS_WKV) bonus[i] = d < D ? a.bonus[(size_t)head * D + d] : 0.0f;
     }
-    for (int base = 0; base < n; base += TT) {
-        const int nt = min(TT, n - base);
-        __syncthreads();                                   // the stage before has been used by everybody
-        for (int e = threadIdx.x; e < nt * DP; e += 128) {
-            const int tt = e / DP, d = e - tt * DP;
-            const size_t row = (size_t)(t0 + base + tt);
-            const bool on = d < D;
-            s_q[tt][d] = on ? a.q[row * a.q_stride + (size_t)qk_head * D + d] : 0.0f;
-            s_k[tt][d] = on ? a.k[row * a.k_stride + (size_t)qk_head * D + d] : 0.0f;
-            s_g[tt][d] = on ? a.g[row * a.g_stride + (size_t)head * D + d] : 0.0f;
+    float* orow = a.out + (size_t)t0 * ((size_t)a.heads * Dv) + (size_t)head * Dv + col;
+    int it = 0;
+    for (int base = 0; base < n; base += TT, ++it) {
+        const int buf = it & 1, nt = min(TT, n - base);
+        if (base + TT < n) {
+            stage(base + TT, buf ^ 1);          // that stage was last read before the barrier that ended the round before
+            asm volatile("cp.async.wait_group 1;" ::: "memory");
+        } else {
+            asm volatile("cp.async.wait_group 0;" ::: "memory");
         }
-        for (int e = threadIdx.x; e < nt * RS_COLS; e += 128) {
-            const int tt = e / RS_COLS, c = e - tt * RS_COLS;
-            s_v[tt][c] = col0 + c < Dv ? a.v[(size_t)(t0 + base + tt) * a.v_stride + (size_t)head * Dv + col0 + c] : 0.0f;
-        }
-        if (MODE == RS_DELTA && threadIdx.x < nt)          // beta arrives as the projection's output: the gate is its sigmoid
-            s_b[threadIdx.x] = 1.0f / (1.0f + expf(-a.beta[(size_t)(t0 + base + threadIdx.x) * a.beta_stride + head]));
         __syncthreads();
+#pragma unroll 2
         for (int tt = 0; tt < nt; ++tt) {
-            const float vj = s_v[tt][warp * (32 / RS_DG) + (lane >> 2)];
+            const float vj = s_v[buf][tt][cl];
             float o;
             if (MODE == RS_DELTA) {
-                float pred = 0.0f, oq = 0.0f, kq = 0.0f;
+                // beta arrives as the projection's output: the gate is its sigmoid
+                const float beta = 1.0f / (1.0f + expf(-s_b[buf][tt]));
+                float pred[2] = {0.0f, 0.0f}, oq[2] = {0.0f, 0.0f}, kq[2] = {0.0f, 0.0f};
 #pragma unroll
                 for (int i4 = 0; i4 < NS / 4; ++i4) {
                     const int d = (i4 * RS_DG + dg) * 4;
-                    const float4 g4 = *reinterpret_cast<const float4*>(&s_g[tt][d]);
-                    const float4 k4 = *reinterpret_cast<const float4*>(&s_k[tt][d]);
-                    const float4 q4 = *reinterpret_cast<const float4*>(&s_q[tt][d]);
+                    const float4 g4 = *reinterpret_cast<const float4*>(&s_g[buf][tt][d]);
+                    const float4 k4 = *reinterpret_cast<const float4*>(&s_k[buf][tt][d]);
+                    const float4 q4 = *reinterpret_cast<const float4*>(&s_q[buf][tt][d]);
                     const float gg[4] = {g4.x, g4.y, g4.z, g4.w}, kk[4] = {k4.x, k4.y, k4.z, k4.w}, qq[4] = {q4.x, q4.y, q4.z, q4.w};
 #pragma unroll
                     for (int e = 0; e < 4; ++e) {
                         const float sd = gg[e] * S[4 * i4 + e];
                         S[4 * i4 + e] = sd;
-                        pred = fmaf(sd, kk[e], pred);
-                        oq = fmaf(sd, qq[e], oq);
-                        kq = fmaf(kk[e], qq[e], kq);
+                        pred[e & 1] = fmaf(sd, kk[e], pred[e & 1]);
+                        oq[e & 1] = fmaf(sd, qq[e], oq[e & 1]);
+                        kq[e & 1] = fmaf(kk[e], qq[e], kq[e & 1]);
                     }
                 }
+                float p = pred[0] + pred[1], oqs = oq[0] + oq[1], kqs = kq[0] + kq[1];
 #pragma unroll
                 for (int off = 1; off < RS_DG; off <<= 1) {
-                    pred += __shfl_xor_sync(0xffffffffu, pred, off);
-                    oq += __shfl_xor_sync(0xffffffffu, oq, off);
-                    kq += __shfl_xor_sync(0xffffffffu, kq, off);
+                    p += __shfl_xor_sync(0xffffffffu, p, off);
+                    oqs += __shfl_xor_sync(0xffffffffu, oqs, off);
+                    kqs += __shfl_xor_sync(0xffffffffu, kqs, off);
                 }
-                const float u = s_b[tt] * (vj - pred);
+                const float u = beta * (vj - p);
 #pragma unroll
                 for (int i4 = 0; i4 < NS / 4; ++i4) {
-                    const float4 k4 = *reinterpret_cast<const float4*>(&s_k[tt][(i4 * RS_DG + dg) * 4]);
+                    const float4 k4 = *reinterpret_cast<const float4*>(&s_k[buf][tt][(i4 * RS_DG + dg) * 4]);
                     S[4 * i4 + 0] = fmaf(k4.x, u, S[4 * i4 + 0]);
                     S[4 * i4 + 1] = fmaf(k4.y, u, S[4 * i4 + 1]);
                     S[4 * i4 + 2] = fmaf(k4.z, u, S[4 * i4 + 2]);
                     S[4 * i4 + 3] = fmaf(k4.w, u, S[4 * i4 + 3]);
                 }
-                o = fmaf(u, kq, oq);
+                o = fmaf(u, kqs, oqs);
             } else {
-                float ro = 0.0f, ruk = 0.0f;
+                float ro[2] = {0.0f, 0.0f}, ruk[2] = {0.0f, 0.0f};
 #pragma unroll
                 for (int i4 = 0; i4 < NS / 4; ++i4) {
                     const int d = (i4 * RS_DG + dg) * 4;
-                    const float4 g4 = *reinterpret_cast<const float4*>(&s_g[tt][d]);
-                    const float4 k4 = *reinterpret_cast<const float4*>(&s_k[tt][d]);
-                    const float4 q4 = *reinterpret_cast<const float4*>(&s_q[tt][d]);
+                    const float4 g4 = *reinterpret_cast<const float4*>(&s_g[buf][tt][d]);
+                    const float4 k4 = *reinterpret_cast<const float4*>(&s_k[buf][tt][d]);
+                    const float4 q4 = *reinterpret_cast<const float4*>(&s_q[buf][tt][d]);
                     const float gg[4] = {g4.x, g4.y, g4.z, g4.w}, kk[4] = {k4.x, k4.y, k4.z, k4.w}, qq[4] = {q4.x, q4.y, q4.z, q4.w};
 #pragma unroll
                     for (int e = 0; e < 4; ++e) {
-                        ro = fmaf(qq[e], S[4 * i4 + e], ro);
-                        ruk = fmaf(qq[e] * bonus[4 * i4 + e], kk[e], ruk);
+                        ro[e & 1] = fmaf(qq[e], S[4 * i4 + e], ro[e & 1]);
+                        ruk[e & 1] = fmaf(qq[e] * bonus[4 * i4 + e], kk[e], ruk[e & 1]);
                         S[4 * i4 + e] = fmaf(gg[e], S[4 * i4 + e], kk[e] * vj);
                     }
                 }
+                float rs = ro[0] + ro[1], us = ruk[0] + ruk[1];
 #pragma unroll
                 for (int off = 1; off < RS_DG; off <<= 1) {
-                    ro += __shfl_xor_sync(0xffffffffu, ro, off);
-                    ruk += __shfl_xor_sync(0xffffffffu, ruk, off);
+                    rs += __shfl_xor_sync(0xffffffffu, rs, off);
+                    us += __shfl_xor_sync(0xffffffffu, us, off);
                 }
-                o = fmaf(vj, ruk, ro);
+                o = fmaf(vj, us, rs);
             }
-            if (dg == 0 && col_ok) a.out[(size_t)(t0 + base + tt) * ((size_t)a.heads * Dv) + (size_t)head * Dv + col] = o;
+            if (dg == 0 && col_ok) orow[(size_t)(base + tt) * ((size_t)a.heads * Dv)] = o;
         }
+        __syncthreads();
     }
     if (col_ok) {
 #pragma unroll

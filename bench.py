@@ -738,6 +738,7 @@ def workload_pogarax(a) -> int:
     import torch
     from airun_b200 import Engine, EngineOptions, StepEntry
     from airun_b200.kernels import fast, ops
+    from airun_b200.parts import latent_attention as latent_part
     pk = peaks()
     T, ctx_len, steps = 2048, 1024, max(8, min(a.steps, 32))
     fp32_peak = 148 * 128 * 2 * 1.965e9          # FMA lanes x 2 x the highest SM clock: nominal, no measured figure
@@ -760,9 +761,9 @@ def workload_pogarax(a) -> int:
                                                              lambda b: 2 * b * ((qr + R + rd) * 4.0 + qr * 2 + (R + rd)), "hbm"),
                     "latent: query parts and rotation": (ops, "latent_query", lambda t: 2 * t * H * ((D + rd) * 4.0 + (D + rd) * 2),
                                                          lambda b: 2 * b * H * ((D + rd) * 4.0 + (D + rd) * 2), "hbm"),
-                    "latent attention": (ops, "latent_attention", lambda t: 2 * H * 2.0 * (2 * R + rd) * win(t),
+                    "latent attention": (fast, "latent_attention_bf16", lambda t: 2 * H * 2.0 * (2 * R + rd) * win(t),
                                          lambda b: 2 * b * min(ctx_len, 2048) * (R + rd) * 2.0, "mixed"),
-                    "products per head (Wuk, Wuv)": (ops, "gemm_simt_batched", lambda t: 2 * t * H * 2.0 * (D * R + R * Dv),
+                    "products per head (Wuk, Wuv)": (latent_part, "head_linear", lambda t: 2 * t * H * 2.0 * (D * R + R * Dv),
                                                      lambda b: 2 * H * (D * R + R * Dv) * 2.0, "tensor"),
                     "delta rule: convolution": (ops, "short_conv", lambda t: 3 * t * (H * 64 + H * 128) * 8.0, lambda b: 3 * b * (H * 64 + H * 128) * 8.0, "hbm"),
                     "low-rank second halves (decays, gate)": (ops, "lowrank_act", lambda t: t * (3 * (H * 64 + H * 128) + W) * 4.0,
