@@ -21,13 +21,15 @@
 __device__ __forceinline__ void lm_cp16(void* smem, const void* gmem) {
     asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"((uint32_t)__cvta_generic_to_shared(smem)), "l"(gmem) : "memory");
 }
-__device__ __forceinline__ void lm_ldsm4(uint32_t (&r)[4], const void* p) {
+// ldmatrix on shared-memory addresses that are worked out once a tile and stepped by plain adds
+__device__ __forceinline__ uint32_t lm_saddr(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
+__device__ __forceinline__ void lm_ldsm4(uint32_t (&r)[4], uint32_t addr) {
     asm volatile("ldmatrix.sync.aligned.m8n8.x4.shared.b16 {%0,%1,%2,%3}, [%4];"
-                 : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]) : "r"((uint32_t)__cvta_generic_to_shared(p)));
+                 : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]) : "r"(addr));
 }
-__device__ __forceinline__ void lm_ldsm4t(uint32_t (&r)[4], const void* p) {
+__device__ __forceinline__ void lm_ldsm4t(uint32_t (&r)[4], uint32_t addr) {
     asm volatile("ldmatrix.sync.aligned.m8n8.x4.trans.shared.b16 {%0,%1,%2,%3}, [%4];"
-                 : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]) : "r"((uint32_t)__cvta_generic_to_shared(p)));
+                 : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]) : "r"(addr));
 }
 __device__ __forceinline__ void lm_mma(float (&c)[4], const uint32_t (&a)[4], uint32_t b0, uint32_t b1) {
     asm volatile("mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};"
@@ -84,6 +86,11 @@ __global__ __launch_bounds__(32 * RW * KW, 1) void latent_attention_mma_kernel(L
         const int tile0 = j_lo / BN, tile_end = p_last / BN + 1;
         const int32_t* bt = a.block_table + (size_t)req * a.max_blocks;
         __syncthreads();                         // the pass before is done with the shared memory
+        // the padding behind a cached row's last element is zero in every stage; the tile loads never copy into it
+        for (int e = threadIdx.x; e < STAGES * BN * (kdp / 8 - chunks); e += NTHREAD) {
+            const int row = e / (kdp / 8 - chunks), ch = chunks + e - row * (kdp / 8 - chunks);
+            *reinterpret_cast<uint4*>(s_k + (size_t)row * kdp + ch * 8) = make_uint4(0, 0, 0, 0);
+        }
         // the queries: row r = (token r / hg, head h0 + r % hg); rows beyond the group and the padding are zero
         for (int r = warp; r < ROWS; r += NWARP) {            // a warp a row: what the row needs is worked out once
             const int tl = r / a.hg, h = h0 + r - tl * a.hg;
@@ -106,11 +113,12 @@ __global__ __launch_bounds__(32 * RW * KW, 1) void latent_attention_mma_kernel(L
                     page = bt[blk];
                     if (page >= a.num_pages) { bad = true; page = -1; }
                 }
-                const __nv_bfloat16* src = a.pool + ((size_t)(page < 0 ? 0 : page) * a.page_size + (j - blk * a.page_size)) * KD;
                 __nv_bfloat16* d = dst + (size_t)kr * kdp;
-                for (int ch = lane; ch < kdp / 8; ch += 32) {
-                    if (page >= 0 && ch < chunks) lm_cp16(d + ch * 8, src + ch * 8);
-                    else *reinterpret_cast<uint4*>(d + ch * 8) = make_uint4(0, 0, 0, 0);
+                if (page >= 0) {
+                    const __nv_bfloat16* src = a.pool + ((size_t)page * a.page_size + (j - blk * a.page_size)) * KD;
+                    for (int ch = lane; ch < chunks; ch += 32) lm_cp16(d + ch * 8, src + ch * 8);
+                } else {
+                    for (int ch = lane; ch < chunks; ch += 32) *reinterpret_cast<uint4*>(d + ch * 8) = make_uint4(0, 0, 0, 0);
                 }
             }
             asm volatile("cp.async.commit_group;" ::: "memory");
@@ -145,16 +153,17 @@ __global__ __launch_bounds__(32 * RW * KW, 1) void latent_attention_mma_kernel(L
             float s[WK / 8][4];
 #pragma unroll
             for (int i = 0; i < WK / 8; ++i) s[i][0] = s[i][1] = s[i][2] = s[i][3] = 0.0f;
-            const __nv_bfloat16* qrow = s_q + (size_t)(rw * 16 + (lane & 15)) * kdp + (lane >> 4) * 8;
-            const __nv_bfloat16* krow = kt + (size_t)((lane & 7) + ((lane >> 4) << 3)) * kdp + ((lane >> 3) & 1) * 8;
+            uint32_t qaddr = lm_saddr(s_q + (size_t)(rw * 16 + (lane & 15)) * kdp + (lane >> 4) * 8);
+            uint32_t kaddr = lm_saddr(kt + (size_t)((lane & 7) + ((lane >> 4) << 3)) * kdp + ((lane >> 3) & 1) * 8);
+            const uint32_t kstep = (uint32_t)(16 * kdp * 2);
 #pragma unroll 4
-            for (int k0 = 0; k0 < a.kd16; k0 += 16) {
+            for (int k0 = 0; k0 < a.kd16; k0 += 16, qaddr += 32, kaddr += 32) {
                 uint32_t af[4];
-                lm_ldsm4(af, qrow + k0);
+                lm_ldsm4(af, qaddr);
 #pragma unroll
                 for (int np = 0; np < WK / 16; ++np) {
                     uint32_t bf[4];
-                    lm_ldsm4(bf, krow + (size_t)np * 16 * kdp + k0);
+                    lm_ldsm4(bf, kaddr + np * kstep);
                     lm_mma(s[2 * np], af, bf[0], bf[1]);
                     lm_mma(s[2 * np + 1], af, bf[2], bf[3]);
                 }
@@ -197,10 +206,12 @@ __global__ __launch_bounds__(32 * RW * KW, 1) void latent_attention_mma_kernel(L
                 psum[i] += __shfl_xor_sync(0xffffffffu, psum[i], 2);
                 l_run[i] = l_run[i] * corr[i] + psum[i];
             }
+            if (corr[0] != 1.0f || corr[1] != 1.0f) {       // once the maxima have settled nothing is rescaled
 #pragma unroll
-            for (int i = 0; i < LM_NT; ++i) { o[i][0] *= corr[0]; o[i][1] *= corr[0]; o[i][2] *= corr[1]; o[i][3] *= corr[1]; }
+                for (int i = 0; i < LM_NT; ++i) { o[i][0] *= corr[0]; o[i][1] *= corr[0]; o[i][2] *= corr[1]; o[i][3] *= corr[1]; }
+            }
             // O += P V, V = the first R elements of the same cached rows
-            const __nv_bfloat16* vrow = kt + (size_t)((lane & 7) + ((lane >> 3) & 1) * 8) * kdp + c0 + (lane >> 4) * 8;
+            const uint32_t vaddr = lm_saddr(kt + (size_t)((lane & 7) + ((lane >> 3) & 1) * 8) * kdp + c0 + (lane >> 4) * 8);
 #pragma unroll
             for (int ks = 0; ks < WK / 16; ++ks) {
                 uint32_t pf[4] = {lm_pack(s[2 * ks][0], s[2 * ks][1]), lm_pack(s[2 * ks][2], s[2 * ks][3]),
@@ -209,7 +220,7 @@ __global__ __launch_bounds__(32 * RW * KW, 1) void latent_attention_mma_kernel(L
                 for (int np = 0; np < LM_NT / 2; ++np) {
                     if (np < n_pairs) {
                         uint32_t vf[4];
-                        lm_ldsm4t(vf, vrow + (size_t)ks * 16 * kdp + np * 16);
+                        lm_ldsm4t(vf, vaddr + ks * kstep + np * 32);
                         lm_mma(o[2 * np], pf, vf[0], vf[1]);
                         lm_mma(o[2 * np + 1], pf, vf[2], vf[3]);
                     }
