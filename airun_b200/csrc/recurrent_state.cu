@@ -238,7 +238,7 @@ __global__ __launch_bounds__(128) void recurrent_state_kernel(RecurrentArgs a) {
     for (int base = 0; base < n; base += TT, ++it) {
         const int buf = it & 1, nt = min(TT, n - base);
         if (base + TT < n) {
-            stage(base + TT, buf ^ 1);          // that stage was last read before the barrier that ended the round before
+            stage(base + TT, buf ^ 1);          // that stage was last read before the barrier that ended the iteration before
             asm volatile("cp.async.wait_group 1;" ::: "memory");
         } else {
             asm volatile("cp.async.wait_group 0;" ::: "memory");
