@@ -119,15 +119,14 @@ AIRUN_EXPORT int airun_token_shift(const float* x, const float* mu, int n_mix, c
 }
 
 // ------------------------------------------------------------------------------------------ the recurrences
-// One block per (request, head, 32 value columns), 128 threads.  A value column is shared by DG = 4 neighbouring
-// lanes, each of which keeps NS key channels of the column's state in registers for the whole step: the sums
-// over key channels are NS multiply-adds in a thread and two shuffles, and nothing but the state chains one token
-// to the next.  The key channels of a lane are every fourth group of four, so the four lanes of a column read
-// neighbouring float4 of the token's q, k and decay from shared memory.  Tokens are staged through shared memory
+// One block per (request, head, 128 / DG value columns), 128 threads.  A value column is shared by DG = 4 or 8
+// neighbouring lanes, each of which keeps NS key channels of the column's state in registers for the whole step: the
+// sums over key channels are NS multiply-adds in a thread and two or three shuffles, and nothing but the state chains
+// one token to the next.  The key channels of a lane are every DG-th group of four, so the lanes of a column read
+// neighbouring float4 of the token's q, k and decay from shared memory.  (Eight lanes a column from 33 key channels
+// on: what bounds a prompt is the chain of its tokens, and a warp's instructions per token halve.)  Tokens are staged through shared memory
 // a few at a time by asynchronous copies into one of two stages.  The block (request, 0, 0) also moves the request's small state on: the last inputs of the
 // short convolution (delta rule) or the last token's x (time mix).
-#define RS_DG 4
-#define RS_COLS 32
 #define RS_TT 16
 #define RS_DELTA 0
 #define RS_WKV 1
@@ -153,16 +152,17 @@ __device__ __forceinline__ void rs_cp16(float* smem, const float* gmem) {
     asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"((uint32_t)__cvta_generic_to_shared(smem)), "l"(gmem) : "memory");
 }
 
-template <int MODE, int NS>
+template <int MODE, int NS, int DG>
 __global__ __launch_bounds__(128) void recurrent_state_kernel(RecurrentArgs a) {
     pdl_trigger();
     pdl_wait();
-    constexpr int DP = NS * RS_DG;
-    constexpr int TT = NS >= 64 ? 4 : NS >= 32 ? 8 : RS_TT;      // tokens of a stage (static shared memory stays under 48 KB)
+    constexpr int DP = NS * DG;
+    constexpr int COLS = 128 / DG;               // value columns of a block: 32 / DG a warp
+    constexpr int TT = DP >= 256 ? 4 : DP >= 128 ? 8 : RS_TT;     // tokens of a stage (static shared memory stays under 48 KB)
     // two stages: the next tokens arrive by asynchronous copies while these are used
-    __shared__ __align__(16) float s_q[2][TT][DP], s_k[2][TT][DP], s_g[2][TT][DP], s_v[2][TT][RS_COLS];
+    __shared__ __align__(16) float s_q[2][TT][DP], s_k[2][TT][DP], s_g[2][TT][DP], s_v[2][TT][COLS];
     __shared__ float s_b[2][TT];
-    const int r = blockIdx.x, head = blockIdx.y, col0 = blockIdx.z * RS_COLS;
+    const int r = blockIdx.x, head = blockIdx.y, col0 = blockIdx.z * COLS;
     const int t0 = a.cu_tokens[r], n = a.cu_tokens[r + 1] - t0;
     if (n <= 0) return;
     const int slot = a.state_slots[r];
@@ -172,18 +172,18 @@ __global__ __launch_bounds__(128) void recurrent_state_kernel(RecurrentArgs a) {
     }
     const int D = a.D, Dv = a.Dv;
     const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
-    const int dg = lane & (RS_DG - 1), cl = warp * (32 / RS_DG) + (lane >> 2), col = col0 + cl;
+    const int dg = lane & (DG - 1), cl = warp * (32 / DG) + lane / DG, col = col0 + cl;
     const bool col_ok = col < Dv;
     const int qk_head = head / a.kv_rep;
     // the padding beyond D and Dv is zero in both stages and is never copied into
     for (int e = threadIdx.x; e < 2 * TT * DP; e += 128) { (&s_q[0][0][0])[e] = 0.0f; (&s_k[0][0][0])[e] = 0.0f; (&s_g[0][0][0])[e] = 0.0f; }
-    for (int e = threadIdx.x; e < 2 * TT * RS_COLS; e += 128) (&s_v[0][0][0])[e] = 0.0f;
+    for (int e = threadIdx.x; e < 2 * TT * COLS; e += 128) (&s_v[0][0][0])[e] = 0.0f;
     __syncthreads();
     const float* qh = a.q + (size_t)qk_head * D;
     const float* kh = a.k + (size_t)qk_head * D;
     const float* gh = a.g + (size_t)head * D;
     const float* vh = a.v + (size_t)head * Dv + col0;
-    const int ncol = min(RS_COLS, Dv - col0);
+    const int ncol = min(COLS, Dv - col0);
     const bool vec = (D % 4 == 0) && ((a.q_stride | a.k_stride | a.g_stride) % 4 == 0) &&
                      ((((uintptr_t)qh | (uintptr_t)kh | (uintptr_t)gh) & 15) == 0);
     const bool vvec = (ncol % 4 == 0) && (a.v_stride % 4 == 0) && (((uintptr_t)vh & 15) == 0);
@@ -229,7 +229,7 @@ __global__ __launch_bounds__(128) void recurrent_state_kernel(RecurrentArgs a) {
     float S[NS], bonus[MODE == RS_WKV ? NS : 1];
 #pragma unroll
     for (int i = 0; i < NS; ++i) {
-        const int d = ((i >> 2) * RS_DG + dg) * 4 + (i & 3);
+        const int d = ((i >> 2) * DG + dg) * 4 + (i & 3);
         S[i] = (col_ok && d < D) ? sbase[(size_t)d * Dv] : 0.0f;
         if (MODE == RS_WKV) bonus[i] = d < D ? a.bonus[(size_t)head * D + d] : 0.0f;
     }
@@ -254,7 +254,7 @@ __global__ __launch_bounds__(128) void recurrent_state_kernel(RecurrentArgs a) {
                 float pred[2] = {0.0f, 0.0f}, oq[2] = {0.0f, 0.0f}, kq[2] = {0.0f, 0.0f};
 #pragma unroll
                 for (int i4 = 0; i4 < NS / 4; ++i4) {
-                    const int d = (i4 * RS_DG + dg) * 4;
+                    const int d = (i4 * DG + dg) * 4;
                     const float4 g4 = *reinterpret_cast<const float4*>(&s_g[buf][tt][d]);
                     const float4 k4 = *reinterpret_cast<const float4*>(&s_k[buf][tt][d]);
                     const float4 q4 = *reinterpret_cast<const float4*>(&s_q[buf][tt][d]);
@@ -270,7 +270,7 @@ __global__ __launch_bounds__(128) void recurrent_state_kernel(RecurrentArgs a) {
                 }
                 float p = pred[0] + pred[1], oqs = oq[0] + oq[1], kqs = kq[0] + kq[1];
 #pragma unroll
-                for (int off = 1; off < RS_DG; off <<= 1) {
+                for (int off = 1; off < DG; off <<= 1) {
                     p += __shfl_xor_sync(0xffffffffu, p, off);
                     oqs += __shfl_xor_sync(0xffffffffu, oqs, off);
                     kqs += __shfl_xor_sync(0xffffffffu, kqs, off);
@@ -278,7 +278,7 @@ __global__ __launch_bounds__(128) void recurrent_state_kernel(RecurrentArgs a) {
                 const float u = beta * (vj - p);
 #pragma unroll
                 for (int i4 = 0; i4 < NS / 4; ++i4) {
-                    const float4 k4 = *reinterpret_cast<const float4*>(&s_k[buf][tt][(i4 * RS_DG + dg) * 4]);
+                    const float4 k4 = *reinterpret_cast<const float4*>(&s_k[buf][tt][(i4 * DG + dg) * 4]);
                     S[4 * i4 + 0] = fmaf(k4.x, u, S[4 * i4 + 0]);
                     S[4 * i4 + 1] = fmaf(k4.y, u, S[4 * i4 + 1]);
                     S[4 * i4 + 2] = fmaf(k4.z, u, S[4 * i4 + 2]);
@@ -289,7 +289,7 @@ __global__ __launch_bounds__(128) void recurrent_state_kernel(RecurrentArgs a) {
                 float ro[2] = {0.0f, 0.0f}, ruk[2] = {0.0f, 0.0f};
 #pragma unroll
                 for (int i4 = 0; i4 < NS / 4; ++i4) {
-                    const int d = (i4 * RS_DG + dg) * 4;
+                    const int d = (i4 * DG + dg) * 4;
                     const float4 g4 = *reinterpret_cast<const float4*>(&s_g[buf][tt][d]);
                     const float4 k4 = *reinterpret_cast<const float4*>(&s_k[buf][tt][d]);
                     const float4 q4 = *reinterpret_cast<const float4*>(&s_q[buf][tt][d]);
@@ -303,7 +303,7 @@ __global__ __launch_bounds__(128) void recurrent_state_kernel(RecurrentArgs a) {
                 }
                 float rs = ro[0] + ro[1], us = ruk[0] + ruk[1];
 #pragma unroll
-                for (int off = 1; off < RS_DG; off <<= 1) {
+                for (int off = 1; off < DG; off <<= 1) {
                     rs += __shfl_xor_sync(0xffffffffu, rs, off);
                     us += __shfl_xor_sync(0xffffffffu, us, off);
                 }
@@ -316,7 +316,7 @@ __global__ __launch_bounds__(128) void recurrent_state_kernel(RecurrentArgs a) {
     if (col_ok) {
 #pragma unroll
         for (int i = 0; i < NS; ++i) {
-            const int d = ((i >> 2) * RS_DG + dg) * 4 + (i & 3);
+            const int d = ((i >> 2) * DG + dg) * 4 + (i & 3);
             if (d < D) sbase[(size_t)d * Dv] = S[i];
         }
     }
@@ -339,28 +339,32 @@ AIRUN_EXPORT int airun_recurrent_state(int mode, const float* q, const float* k,
                                        const float* beta, long long beta_stride, const float* bonus, float* state,
                                        long long slot_stride, int max_slots, const int32_t* cu_tokens, const int32_t* state_slots,
                                        int num_reqs, float* out, int heads, int kv_rep, int D, int Dv, const float* tail_src,
-                                       long long tail_src_stride, long long tail_off, int tail_rows, int tail_width, int* err,
-                                       cudaStream_t stream) {
+                                       long long tail_src_stride, long long tail_off, int tail_rows, int tail_width,
+                                       int long_chains, int* err, cudaStream_t stream) {
     if (num_reqs < 0 || heads <= 0 || heads > 65535 || kv_rep <= 0 || heads % kv_rep || D <= 0 || D > 256 || Dv <= 0 || !state ||
         !cu_tokens || !state_slots || !err || !q || !k || !v || !g || !out || slot_stride < (long long)heads * D * Dv)
         return AIRUN_ERR_ARG;
     if (mode == RS_DELTA ? !beta : !bonus) return AIRUN_ERR_ARG;
     if (tail_rows < 0 || (tail_rows > 0 && (!tail_src || tail_width <= 0))) return AIRUN_ERR_ARG;
     if (num_reqs == 0) return AIRUN_OK;
-    const int tiles = ceil_div_i(Dv, RS_COLS);
+    // lanes that share a value column: 8 where requests bring many tokens (the chain of a prompt's tokens bounds the
+    // step, and a warp's instructions per token halve), 4 where most bring one (the state is read and written once, in
+    // wider pieces)
+    const int dg = (D <= 32 || !long_chains) ? 4 : 8;
+    const int tiles = ceil_div_i(Dv, 128 / dg);
     if (tiles > 65535) return AIRUN_ERR_ARG;
     RecurrentArgs a = {q, k, v, g, q_stride, k_stride, v_stride, g_stride, beta, beta_stride, bonus, state, slot_stride, max_slots,
                        cu_tokens, state_slots, out, heads, kv_rep, D, Dv, tail_src, tail_src_stride, tail_off, tail_rows,
                        tail_width, err};
     dim3 grid(num_reqs, heads, tiles);
-#define RS_LAUNCH(NS) \
-    do { if (mode == RS_DELTA) airun_launch(recurrent_state_kernel<RS_DELTA, NS>, grid, dim3(128), 0, stream, a); \
-         else airun_launch(recurrent_state_kernel<RS_WKV, NS>, grid, dim3(128), 0, stream, a); } while (0)
-    if (D <= 16) RS_LAUNCH(4);
-    else if (D <= 32) RS_LAUNCH(8);
-    else if (D <= 64) RS_LAUNCH(16);
-    else if (D <= 128) RS_LAUNCH(32);
-    else RS_LAUNCH(64);
+#define RS_LAUNCH(NS, DG) \
+    do { if (mode == RS_DELTA) airun_launch(recurrent_state_kernel<RS_DELTA, NS, DG>, grid, dim3(128), 0, stream, a); \
+         else airun_launch(recurrent_state_kernel<RS_WKV, NS, DG>, grid, dim3(128), 0, stream, a); } while (0)
+    if (D <= 16) RS_LAUNCH(4, 4);
+    else if (D <= 32) RS_LAUNCH(8, 4);
+    else if (D <= 64) { if (dg == 8) RS_LAUNCH(8, 8); else RS_LAUNCH(16, 4); }
+    else if (D <= 128) { if (dg == 8) RS_LAUNCH(16, 8); else RS_LAUNCH(32, 4); }
+    else { if (dg == 8) RS_LAUNCH(32, 8); else RS_LAUNCH(64, 4); }
 #undef RS_LAUNCH
     return airun_launch_status();
 }

@@ -566,11 +566,12 @@ def recurrent_state(mode: int, q: torch.Tensor, k: torch.Tensor, v: torch.Tensor
     f = _fn("recurrent_state", "airun_recurrent_state",
             [c_int, c_void_p, c_void_p, c_void_p, c_void_p, c_longlong, c_longlong, c_longlong, c_longlong, c_void_p, c_longlong,
              c_void_p, c_void_p, c_longlong, c_int, c_void_p, c_void_p, c_int, c_void_p, c_int, c_int, c_int, c_int, c_void_p,
-             c_longlong, c_longlong, c_int, c_int, c_void_p, c_void_p])
+             c_longlong, c_longlong, c_int, c_int, c_int, c_void_p, c_void_p])
+    long_chains = 1 if T > 2 * int(ctx.num_reqs) else 0          # requests bring many tokens each, not one
     _check(f(int(mode), _p(q), _p(k), _p(v), _p(g), _row_stride(q), _row_stride(k), _row_stride(v), _row_stride(g), _p(beta), bs,
              _p(bonus), _p(state), state.stride(0), state.shape[0], _p(ctx.cu_tokens), _p(ctx.state_slots), int(ctx.num_reqs),
-             _p(out), heads, kv_rep, D, Dv, _p(tail_src), ts, int(tail_off), int(tail_rows), tw, _p(ctx.err), _stream()),
-           "recurrent_state")
+             _p(out), heads, kv_rep, D, Dv, _p(tail_src), ts, int(tail_off), int(tail_rows), tw, long_chains, _p(ctx.err),
+             _stream()), "recurrent_state")
 
 
 # ---------------------------------------------------------------- attention over a cached latent
