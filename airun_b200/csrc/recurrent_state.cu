@@ -175,15 +175,17 @@ __global__ __launch_bounds__(128) void recurrent_state_kernel(RecurrentArgs a) {
     const int dg = lane & (DG - 1), cl = warp * (32 / DG) + lane / DG, col = col0 + cl;
     const bool col_ok = col < Dv;
     const int qk_head = head / a.kv_rep;
-    // the padding beyond D and Dv is zero in both stages and is never copied into
-    for (int e = threadIdx.x; e < 2 * TT * DP; e += 128) { (&s_q[0][0][0])[e] = 0.0f; (&s_k[0][0][0])[e] = 0.0f; (&s_g[0][0][0])[e] = 0.0f; }
-    for (int e = threadIdx.x; e < 2 * TT * COLS; e += 128) (&s_v[0][0][0])[e] = 0.0f;
-    __syncthreads();
+    const int ncol = min(COLS, Dv - col0);
+    // the padding beyond D and Dv is zero in both stages and is never copied into (nothing to do when there is none)
+    if (D < DP || ncol < COLS) {
+        for (int e = threadIdx.x; e < 2 * TT * DP; e += 128) { (&s_q[0][0][0])[e] = 0.0f; (&s_k[0][0][0])[e] = 0.0f; (&s_g[0][0][0])[e] = 0.0f; }
+        for (int e = threadIdx.x; e < 2 * TT * COLS; e += 128) (&s_v[0][0][0])[e] = 0.0f;
+        __syncthreads();
+    }
     const float* qh = a.q + (size_t)qk_head * D;
     const float* kh = a.k + (size_t)qk_head * D;
     const float* gh = a.g + (size_t)head * D;
     const float* vh = a.v + (size_t)head * Dv + col0;
-    const int ncol = min(COLS, Dv - col0);
     const bool vec = (D % 4 == 0) && ((a.q_stride | a.k_stride | a.g_stride) % 4 == 0) &&
                      ((((uintptr_t)qh | (uintptr_t)kh | (uintptr_t)gh) & 15) == 0);
     const bool vvec = (ncol % 4 == 0) && (a.v_stride % 4 == 0) && (((uintptr_t)vh & 15) == 0);
