@@ -1,6 +1,7 @@
 // A routed feed-forward: every token goes to the `top` experts with the largest scores.
 //
-//   z = Wr h (float32),  s = sigmoid(z) or softmax(z);  the `top` largest s (equal scores: the lower id first)
+//   z = Wr h (float32),  s = sigmoid(z) or softmax(z);  the `top` largest s (equal scores: the lower id first),
+//   found as the `top` largest z: the order is the same, and float32 scores that saturate at 1 are not told apart
 //   weight = s of the chosen expert, divided by the sum of the chosen ones when `renorm`
 // The rows of a step are then sorted by expert so that every expert's rows are one segment of a buffer and a
 // grouped product (gemm_simt.cu) runs each segment against its expert's matrices:
@@ -34,18 +35,16 @@ __global__ __launch_bounds__(128) void moe_route_kernel(
     }
     for (int e = lane; e < E; e += 32) s_score[e] = z[(size_t)t * E + e];
     __syncwarp();
+    // The choice is made on the logits: sigmoid and softmax rise with them, so the order is the same, and two large
+    // logits whose scores both round to 1 are still told apart.  The score of a chosen expert is worked out afterwards.
+    float smax = -INFINITY, ssum = 1.0f;
     if (softmax_scores) {
-        float m = -INFINITY;
-        for (int e = lane; e < E; e += 32) m = fmaxf(m, s_score[e]);
-        m = warp_max(m);
-        float sum = 0.0f;
-        for (int e = lane; e < E; e += 32) { const float p = expf(s_score[e] - m); s_score[e] = p; sum += p; }
-        sum = warp_sum(sum);
-        for (int e = lane; e < E; e += 32) s_score[e] /= sum;
-    } else {
-        for (int e = lane; e < E; e += 32) s_score[e] = 1.0f / (1.0f + expf(-s_score[e]));
+        for (int e = lane; e < E; e += 32) smax = fmaxf(smax, s_score[e]);
+        smax = warp_max(smax);
+        ssum = 0.0f;
+        for (int e = lane; e < E; e += 32) ssum += expf(s_score[e] - smax);
+        ssum = warp_sum(ssum);
     }
-    __syncwarp();
     float total = 0.0f;
     for (int k = 0; k < top; ++k) {
         float best = -INFINITY;
@@ -60,11 +59,12 @@ __global__ __launch_bounds__(128) void moe_route_kernel(
             const int oa = __shfl_xor_sync(0xffffffffu, arg, o);
             if (ob > best || (ob == best && oa < arg)) { best = ob; arg = oa; }
         }
-        if (arg >= E) arg = 0;                              // a row of NaN scores: still a valid expert
-        total += best;
+        if (arg >= E) arg = 0;                              // a row of NaN logits: still a valid expert
+        const float score = softmax_scores ? expf(best - smax) / ssum : 1.0f / (1.0f + expf(-best));
+        total += score;
         if (lane == 0) {
             ids[(size_t)t * top + k] = arg;
-            wts[(size_t)t * top + k] = best;
+            wts[(size_t)t * top + k] = score;
             rank[(size_t)t * top + k] = atomicAdd(&counts[arg], 1);
             s_score[arg] = -INFINITY;
         }

@@ -1,7 +1,8 @@
 """Routed experts: a feed-forward made of many small gated units of which every token uses a few.
 
     z = Wr h  (float32),   s = sigmoid(z)  (or softmax(z) with ``scores="softmax"``)
-    the ``top`` experts with the largest s are chosen (equal scores: the lower id)
+    the ``top`` experts with the largest s are chosen (equal scores: the lower id); the kernel orders them by z,
+    which orders them as s does and still tells apart two large logits whose float32 scores both round to 1
     weight_e = s_e, divided by the sum over the chosen ones when ``renormalize``
     out = sum_e expert_e(weight_e * h)          (``weight_on="input"``: the weight scales what the expert reads)
     out = sum_e weight_e * expert_e(h)          (``weight_on="output"``)

@@ -828,3 +828,18 @@ def test_tensor_core_latent_attention(H, R, rd, page, window, single):
     assert int(ctx.err.item()) == 0
     want = torch.cat([plain_latent_rows(*reqs[r], H, R, rd, 0.2, window, sink, P.to_bf16_and_back)[a:b] for r, (a, b) in enumerate(spans)])
     assert torch.allclose(out.cpu().double(), want, atol=3e-2, rtol=3e-2)
+
+
+@gpu
+def test_router_tells_apart_scores_that_saturate():
+    """Logits of 17 and more all have the float32 sigmoid 1.0: the experts are still chosen in the order of the logits,
+    as the exact scores order them."""
+    from airun_b200.kernels import ops
+    z = torch.tensor([[17.5, -2.0, 21.0, 19.0, 3.0], [30.0, 30.5, -1.0, 29.0, 40.0]])
+    T, E, top = z.shape[0], z.shape[1], 3
+    ids, rank = (torch.zeros(T, top, dtype=torch.int32, device="cuda") for _ in range(2))
+    wts = torch.zeros(T, top, device="cuda")
+    counts, seg = torch.zeros(E, dtype=torch.int32, device="cuda"), torch.zeros(E + 1, dtype=torch.int32, device="cuda")
+    ops.moe_route(dev(z), top, False, False, torch.zeros(T, dtype=torch.int32, device="cuda"), ids, wts, rank, counts, seg)
+    assert ids.cpu().tolist() == [[2, 3, 0], [4, 1, 0]]
+    assert torch.allclose(wts.cpu().double(), torch.sigmoid(z.double()).gather(1, ids.cpu().long()), atol=1e-6)
